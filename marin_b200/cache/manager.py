@@ -10,7 +10,7 @@ cache has one page table per sequence and no sharing between sequences
 is this engine's own design.
 
 Device layout of a group: ``K, V : [entries, pages, kv_heads, page_size, head_dim]`` so that
-one (page, kv head) tile is contiguous.
+one (page, kv head) tile is contiguous (values have their own head size where a mixer says so).
 """
 from __future__ import annotations
 
@@ -172,9 +172,9 @@ class CacheManager:
 
     def allocate(self, device, dtype: torch.dtype) -> None:
         for g in self.groups:
-            shape = (len(g.entries), self.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim)
-            g.k = torch.zeros(shape, device=device, dtype=dtype)
-            g.v = torch.zeros(shape, device=device, dtype=dtype)
+            shape = (len(g.entries), self.num_pages, g.need.kv_heads, self.page_size)
+            g.k = torch.zeros(shape + (g.need.head_dim,), device=device, dtype=dtype)
+            g.v = torch.zeros(shape + (g.need.value_dim,), device=device, dtype=dtype)
         # one slot more than there can be requests: the rows that pad a captured batch read and write the spare slot
         for i, need in self.state_needs.items():
             self.state[i] = torch.zeros((self.max_requests + 1, *need.shape), device=device, dtype=need.dtype)

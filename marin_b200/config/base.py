@@ -99,4 +99,12 @@ def load_config(model_dir: str) -> ModelConfig:
     if os.path.exists(gen_path):
         generation = read_json(gen_path)
     arch = architecture_for(raw)
-    return arch.config_class.from_dict(raw, generation)
+    config = arch.config_class.from_dict(raw, generation)
+    if arch.resolve_shapes is not None:
+        # sizes that only the checkpoint's tensors give (read from the files' headers; no tensor is loaded)
+        from ..weights.loader import checkpoint_shapes
+
+        shapes = checkpoint_shapes(model_dir)
+        if shapes:
+            config = arch.resolve_shapes(config, shapes)
+    return config

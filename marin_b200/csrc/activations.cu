@@ -1,0 +1,170 @@
+// Norms and activations that are not RMSNorm or SwiGLU: Dynamic Tanh, PolyNorm, a gated RMS norm over the whole row,
+// the mixing of a row with the row before it (token shift), and a tanh cap on the logits.  Sums, norms and the
+// transcendental functions are float32 whatever the activation dtype; every kernel takes its sizes as arguments.
+#define MB_LIB "activations"
+#define MB_LIB_ID 8
+#include "common.cuh"
+#include "launch.cuh"
+
+// ---- Dynamic Tanh: out[t, i] = tanh(alpha * x[t, i]) * w[i] + b[i]; no statistic of the row enters ---------------------
+template <typename TO>
+__global__ void dyt_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                           const float* __restrict__ alpha, TO* __restrict__ out, size_t total, int n) {
+    PDL_ENTER();
+    x = pdl_fresh(x);
+    const float a = alpha[0];
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const int i = (int)(idx % (size_t)n);
+        out[idx] = from_f32<TO>(fmaf(tanhf(a * x[idx]), w[i], b != nullptr ? b[i] : 0.0f));
+    }
+}
+
+static inline int blocks_for(size_t total, int threads) {
+    const size_t want = (total + threads - 1) / threads;
+    return (int)(want < (size_t)148 * 16 ? want : (size_t)148 * 16);
+}
+
+MB_API int mb_dyt(const float* x, const float* w, const float* b, const float* alpha, void* out, int out_dtype, int rows, int n,
+                  cudaStream_t s) {
+    const size_t total = (size_t)rows * n;
+    if (total == 0) return 0;
+    if (out_dtype == MB_F32) return launch_kernel(dyt_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, x, w, b, alpha, (float*)out, total, n);
+    if (out_dtype == MB_BF16) return launch_kernel(dyt_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, x, w, b, alpha, (bf16*)out, total, n);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e, N(y) = y / sqrt(mean(y^2) + eps) over the row ---------------------
+// One block per row; the three sums of squares (z^2, z^4, z^6) in one pass, the row read a second time for the result.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) polynorm_kernel(const TI* __restrict__ z, const float* __restrict__ coef, float eps,
+                                                       TO* __restrict__ out, int n) {
+    PDL_ENTER();
+    z = pdl_fresh(z);
+    __shared__ float scratch[32];
+    const TI* row = z + (size_t)blockIdx.x * n;
+    TO* dst = out + (size_t)blockIdx.x * n;
+    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = to_f32(row[i]), v2 = v * v;
+        s1 += v2;
+        s2 += v2 * v2;
+        s3 += v2 * v2 * v2;
+    }
+    s1 = block_sum(s1, scratch);
+    s2 = block_sum(s2, scratch);
+    s3 = block_sum(s3, scratch);
+    const float r1 = coef[0] / sqrtf(s1 / (float)n + eps), r2 = coef[1] / sqrtf(s2 / (float)n + eps),
+                r3 = coef[2] / sqrtf(s3 / (float)n + eps), e = coef[3];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = to_f32(row[i]), v2 = v * v;
+        dst[i] = from_f32<TO>(r1 * v + r2 * v2 + r3 * (v2 * v) + e);
+    }
+}
+
+MB_API int mb_polynorm(const void* z, int z_dtype, const float* coef, float eps, void* out, int out_dtype, int rows, int n,
+                       cudaStream_t s) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (z_dtype == MB_F32 && out_dtype == MB_F32)
+        return launch_kernel(polynorm_kernel<float, float>, rows, 256, 0, s, 0, (const float*)z, coef, eps, (float*)out, n);
+    if (z_dtype == MB_F32 && out_dtype == MB_BF16)
+        return launch_kernel(polynorm_kernel<float, bf16>, rows, 256, 0, s, 0, (const float*)z, coef, eps, (bf16*)out, n);
+    if (z_dtype == MB_BF16 && out_dtype == MB_BF16)
+        return launch_kernel(polynorm_kernel<bf16, bf16>, rows, 256, 0, s, 0, (const bf16*)z, coef, eps, (bf16*)out, n);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- gated RMS norm over the whole row: out = o / sqrt(mean(o^2) + eps) * w * gate(g) ---------------------------------
+// o is float32 (what a recurrence leaves); g is read with a stride (it may be a slice of a wider row); gate: 0 sigmoid,
+// 1 silu, 2 none (g may then be null).
+template <typename T>
+__global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w,
+                                                            const T* __restrict__ g, int g_stride, int gate, float eps,
+                                                            T* __restrict__ out, int n) {
+    PDL_ENTER();
+    o = pdl_fresh(o);
+    g = pdl_fresh(g);
+    __shared__ float scratch[32];
+    const float* row = o + (size_t)blockIdx.x * n;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = row[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float y = row[i] * scale * w[i];
+        if (gate != 2) {
+            const float z = to_f32(g[(size_t)blockIdx.x * g_stride + i]);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            y *= gate == 0 ? sg : z * sg;
+        }
+        out[(size_t)blockIdx.x * n + i] = from_f32<T>(y);
+    }
+}
+
+MB_API int mb_gated_rmsnorm(const float* o, const float* w, const void* g, int g_stride, int gate, float eps, void* out, int dtype,
+                            int rows, int n, cudaStream_t s) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (gate < 0 || gate > 2 || (gate != 2 && g == nullptr)) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32) return launch_kernel(gated_rmsnorm_kernel<float>, rows, 256, 0, s, 0, o, w, (const float*)g, g_stride, gate, eps, (float*)out, n);
+    if (dtype == MB_BF16) return launch_kernel(gated_rmsnorm_kernel<bf16>, rows, 256, 0, s, 0, o, w, (const bf16*)g, g_stride, gate, eps, (bf16*)out, n);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- token shift: out[m, t, :] = h[t] + (h'[t] - h[t]) * mu[m], h' the row before in the same sequence ------------------
+// The row before a step's first token of a request is what the request's state keeps (zeros at admission): `carry`
+// points at it inside the state, one row of `state_stride` floats per slot.  Nothing is written to the state here (the
+// first token's block of a request reads what its last token's block would write): the kernel that runs the recurrence
+// stores the new last row.
+template <typename T>
+__global__ void shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ carry, long long state_stride,
+                                 const int* __restrict__ req_index, const int* __restrict__ cu_tokens,
+                                 const int* __restrict__ state_slots, const float* __restrict__ mu, int mixes,
+                                 T* __restrict__ out, int tokens, int n) {
+    PDL_ENTER();
+    h = pdl_fresh(h);
+    carry = pdl_fresh(carry);
+    const int t = blockIdx.x;
+    const int req = req_index[t];
+    const bool first = cu_tokens[req] == t;
+    const float* before = carry + (size_t)state_slots[req] * state_stride;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float now = to_f32(h[(size_t)t * n + i]);
+        const float prev = first ? before[i] : to_f32(h[(size_t)(t - 1) * n + i]);
+        const float d = prev - now;
+        for (int m = 0; m < mixes; ++m)
+            out[((size_t)m * tokens + t) * n + i] = from_f32<T>(fmaf(d, mu[(size_t)m * n + i], now));
+    }
+}
+
+MB_API int mb_shift_mix(const void* h, int dtype, const float* carry, long long state_stride, const int* req_index,
+                        const int* cu_tokens, const int* state_slots, const float* mu, int mixes, void* out, int tokens, int n,
+                        cudaStream_t s) {
+    if (tokens <= 0 || n <= 0 || mixes <= 0) return 0;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (dtype == MB_F32)
+        return launch_kernel(shift_mix_kernel<float>, tokens, threads, 0, s, 0, (const float*)h, carry, state_stride, req_index, cu_tokens,
+                             state_slots, mu, mixes, (float*)out, tokens, n);
+    if (dtype == MB_BF16)
+        return launch_kernel(shift_mix_kernel<bf16>, tokens, threads, 0, s, 0, (const bf16*)h, carry, state_stride, req_index, cu_tokens,
+                             state_slots, mu, mixes, (bf16*)out, tokens, n);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- tanh (in place, any dtype) and the cap on logits: x <- cap * tanh(x / cap) -----------------------------------------
+template <typename T>
+__global__ void tanh_kernel(T* __restrict__ x, size_t total, float cap) {
+    PDL_ENTER();
+    x = pdl_fresh(x);
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) x[idx] = from_f32<T>(cap * tanhf(to_f32(x[idx]) / cap));
+}
+
+MB_API int mb_tanh_cap(void* x, int dtype, size_t total, float cap, cudaStream_t s) {
+    if (total == 0) return 0;
+    if (!(cap > 0.0f)) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32) return launch_kernel(tanh_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (float*)x, total, cap);
+    if (dtype == MB_BF16) return launch_kernel(tanh_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, total, cap);
+    return MB_ERR_BAD_DTYPE;
+}

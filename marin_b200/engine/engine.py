@@ -73,7 +73,7 @@ def load_random(model: Model, seed: int, rt: Runtime) -> None:
             spec = super().pop(name, *default)
             if not isinstance(spec, TensorSpec):
                 return spec
-            return random_tensor(spec, seed, rt.dtype if spec.role != "norm" else torch.float32, dev)
+            return random_tensor(spec, seed, rt.dtype if spec.role not in ("norm", "bias") else torch.float32, dev)
 
     model.load(Drawn({spec.name: spec for spec in model.tensor_specs()}), rt)
     if rt.device.type == "cuda":

@@ -152,6 +152,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_simple": ["attention_simple.cu"],
     "mb_sampling": ["sampling.cu"],
     "mb_gemm_tc": ["gemm_tc.cu"],
+    "mb_activations": ["activations.cu"],
+    "mb_recurrent": ["recurrent.cu"],
+    "mb_attention_sigmoid": ["attention_sigmoid.cu"],
     "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp", "host/safetensors.cpp"],
 }
 

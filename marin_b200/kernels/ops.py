@@ -109,12 +109,18 @@ def _lib(name: str):
     return build.load(name, build.LIBRARIES[name])
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    _need_cuda(ids, table, out)
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
+          positions: Optional[torch.Tensor] = None) -> None:
+    """``out[t] = float32(table[ids[t]])``, plus ``float32(pos_table[positions[t]])`` where a learned position table is given."""
+    _need_cuda(ids, table, out, pos_table, positions)
     T, h = out.shape
     assert ids.dtype == torch.int32 and ids.numel() == T and table.shape[1] == h and out.dtype == torch.float32
-    _cost(T * h * table.element_size() + _size(out) + _size(ids))
-    _check(_lib("mb_elementwise").mb_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), _c_int(T), _c_int(h), _stream()), "embed")
+    if pos_table is not None:
+        assert positions is not None and positions.dtype == torch.int32 and positions.numel() == T
+        assert pos_table.dtype == table.dtype and pos_table.shape[1] == h
+    _cost(T * h * table.element_size() * (2 if pos_table is not None else 1) + _size(out) + _size(ids))
+    _check(_lib("mb_elementwise").mb_embed(_ptr(ids), _ptr(table), _code(table), _ptr(pos_table), _ptr(positions if pos_table is not None else None),
+                                          _ptr(out), _c_int(T), _c_int(h), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, unit_offset: bool = False) -> None:
@@ -815,3 +821,159 @@ def sample(logits: torch.Tensor, usable: torch.Tensor, temperature: torch.Tensor
     _cost(_size(logits))
     _check(_lib("mb_sampling").mb_sample(_ptr(logits), _c_int(rows), _c_int(vocab), _ptr(usable), _ptr(temperature), _ptr(top_k),
                                         _ptr(top_p), _ptr(uniform), _ptr(out), _ptr(s.report), _ptr(s.error), _stream()), "sample")
+
+
+# ---- norms and activations beside RMSNorm and SwiGLU (csrc/activations.cu) ---------------------------------------------
+
+def dynamic_tanh(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], alpha: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = tanh(alpha * x) * weight + bias`` element by element; ``x`` float32 ``[rows, n]``, ``alpha`` one float32 on the device."""
+    _need_cuda(x, weight, bias, alpha, out)
+    rows, n = x.shape
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == n and out.shape == x.shape
+    assert alpha.dtype == torch.float32 and alpha.numel() == 1 and (bias is None or (bias.dtype == torch.float32 and bias.numel() == n))
+    _cost(_size(x) + _size(out) + 2 * _size(weight), 4.0 * rows * n)
+    _check(_lib("mb_activations").mb_dyt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(out), _code(out), _c_int(rows), _c_int(n),
+                                        _stream()), "dynamic tanh")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` with ``coef = (a, b, c, e)`` (float32 on the device) and ``N`` a row divided by
+    its root mean square (``eps`` under the root); sums in float32."""
+    _need_cuda(z, coef, out)
+    rows, n = z.shape
+    assert coef.dtype == torch.float32 and coef.numel() == 4 and out.shape == z.shape
+    _cost(2 * _size(z) + _size(out), 12.0 * rows * n)
+    _check(_lib("mb_activations").mb_polynorm(_ptr(z), _code(z), _ptr(coef), _c_float(eps), _ptr(out), _code(out), _c_int(rows), _c_int(n),
+                                             _stream()), "polynorm")
+
+
+GATES = {"sigmoid": 0, "silu": 1, None: 2}
+
+
+def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, gate_rows: Optional[torch.Tensor], gate: Optional[str], eps: float,
+                  out: torch.Tensor) -> None:
+    """``out = o / sqrt(mean(o^2) + eps) * weight * gate(gate_rows)`` over whole rows; ``o`` float32 ``[rows, n]``, ``gate_rows``
+    ``[rows, n]`` in the activation dtype (it may be a column slice of a wider matrix), ``gate`` "sigmoid", "silu" or None."""
+    _need_cuda(o, weight, out)
+    rows, n = o.shape
+    assert o.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == n and tuple(out.shape) == (rows, n)
+    stride = 0
+    if gate is not None:
+        assert gate_rows is not None and gate_rows.is_cuda and gate_rows.dtype == out.dtype and tuple(gate_rows.shape) == (rows, n)
+        assert gate_rows.stride(1) == 1
+        stride = gate_rows.stride(0)
+    _cost(_size(o) + 2 * _size(out), 8.0 * rows * n)
+    _check(_lib("mb_activations").mb_gated_rmsnorm(_ptr(o), _ptr(weight), _ptr(gate_rows if gate is not None else None), _c_int(stride),
+                                                  _c_int(GATES[gate]), _c_float(eps), _ptr(out), _code(out), _c_int(rows), _c_int(n),
+                                                  _stream()), "gated rmsnorm")
+
+
+def shift_mix(h: torch.Tensor, carry: torch.Tensor, ctx, slots: torch.Tensor, mu: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[m, t] = h[t] + (h'[t] - h[t]) * mu[m]`` with ``h'`` the row before in the same sequence; before a request's first
+    token of this step it is the row its state keeps: ``carry`` is that part of the state tensor, float32 ``[slots, n]`` (a
+    column slice: its row stride is the state's)."""
+    _need_cuda(h, mu, out, slots)
+    T, n = h.shape
+    mixes = mu.shape[0]
+    assert carry.is_cuda and carry.dtype == torch.float32 and carry.shape[1] == n and carry.stride(1) == 1
+    assert mu.dtype == torch.float32 and tuple(mu.shape) == (mixes, n) and tuple(out.shape) == (mixes, T, n) and out.dtype == h.dtype
+    _cost(_size(h) + _size(out), 2.0 * mixes * T * n)
+    _check(_lib("mb_activations").mb_shift_mix(_ptr(h), _code(h), _c_void_p(carry.data_ptr()), ctypes.c_longlong(carry.stride(0)),
+                                              _ptr(ctx.req_index), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(mu), _c_int(mixes), _ptr(out),
+                                              _c_int(T), _c_int(n), _stream()), "token shift")
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> None:
+    """``x <- cap * tanh(x / cap)`` in place (``cap = 1``: a plain tanh)."""
+    _need_cuda(x)
+    _cost(2 * _size(x), 2.0 * x.numel())
+    _check(_lib("mb_activations").mb_tanh_cap(_ptr(x), _code(x), _c_size_t(x.numel()), _c_float(cap), _stream()), "tanh cap")
+
+
+# ---- recurrences with a matrix state per head (csrc/recurrent.cu) ------------------------------------------------------
+
+def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx,
+                          slots: torch.Tensor, o: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+    """``S_t = decay_h S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` per head over each request's tokens of the step, from and into
+    ``state[slot]`` (float32 ``[slots, heads, dim, vdim]``).  ``q``, ``k``, ``v`` are column slices of one projection (before
+    their silu, which the kernel applies); ``o`` float32 ``[T, heads * vdim]``."""
+    _need_cuda(decay, state, o, slots)
+    T = q.shape[0]
+    stride = q.stride(0)
+    assert q.is_cuda and q.dtype == k.dtype == v.dtype and k.stride(0) == stride and v.stride(0) == stride
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    assert tuple(q.shape) == (T, heads * dim) and tuple(k.shape) == (T, heads * dim) and tuple(v.shape) == (T, heads * vdim)
+    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, vdim) and decay.dtype == torch.float32 and decay.numel() == heads
+    assert o.dtype == torch.float32 and tuple(o.shape) == (T, heads * vdim)
+    R = ctx.num_requests
+    _cost(T * heads * (2 * dim + vdim) * q.element_size() + _size(o) + 2.0 * R * heads * dim * vdim * 4, 4.0 * T * heads * dim * vdim)
+    _check(_lib("mb_recurrent").mb_linear_attention_scan(
+        _c_void_p(q.data_ptr()), _c_void_p(k.data_ptr()), _c_void_p(v.data_ptr()), _code(q), _c_int(stride), _ptr(decay), _ptr(state),
+        _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R), _c_int(heads), _c_int(dim), _c_int(vdim), _stream()), "linear attention (scan)")
+
+
+def wkv_scan(r, k, v, g, wraw, w0, u, norm_w, eps: float, state: torch.Tensor, carry: torch.Tensor, h: torch.Tensor, ctx,
+             slots: torch.Tensor, out: torch.Tensor, heads: int, dim: int) -> None:
+    """``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(w_t) S_(t-1) + k_t v_t^T`` with ``w = exp(-exp(wraw + w0))``,
+    each head's ``o`` divided by its root mean square, times ``norm_w``, times ``silu(g)``.  ``state`` and ``carry`` are column
+    slices of one float32 state tensor (``[slots, heads * dim * dim]`` and ``[slots, width]``); the last row of ``h`` of every
+    request goes to ``carry``."""
+    _need_cuda(r, k, v, g, wraw, w0, u, norm_w, h, out, slots)
+    T, n = r.shape
+    assert n == heads * dim and all(tuple(x.shape) == (T, n) and x.dtype == r.dtype for x in (k, v, g, out))
+    assert wraw.dtype == torch.float32 and tuple(wraw.shape) == (T, n) and all(x.dtype == torch.float32 and x.numel() == n for x in (w0, u, norm_w))
+    assert state.dtype == torch.float32 and carry.dtype == torch.float32 and state.stride(0) == carry.stride(0)
+    assert state.shape[1] == heads * dim * dim and carry.shape[1] == h.shape[1] and h.dtype == r.dtype and h.shape[0] == T
+    R = ctx.num_requests
+    _cost(5 * _size(r) + _size(wraw) + 2.0 * R * heads * dim * dim * 4, 6.0 * T * heads * dim * dim)
+    _check(_lib("mb_recurrent").mb_wkv_scan(
+        _ptr(r), _ptr(k), _ptr(v), _ptr(g), _code(r), _ptr(wraw), _ptr(w0), _ptr(u), _ptr(norm_w), _c_float(eps),
+        _c_void_p(state.data_ptr()), _c_void_p(carry.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(h), _c_int(h.shape[1]),
+        _ptr(ctx.cu_tokens), _ptr(slots), _ptr(out), _c_int(R), _c_int(heads), _c_int(dim), _stream()), "wkv (scan)")
+
+
+# ---- attention with sigmoid weights (csrc/attention_sigmoid.cu) ---------------------------------------------------------
+
+def qkv_heads_sigmoid(qkv, q_out, q_weight, k_weight, eps: float, positions, temp_coef: float, temp_every: int, slot_mapping,
+                      k_cache, v_cache, H: int, K: int, d: int, dv: int, write_kv: bool = True) -> None:
+    """Finishes the heads of a fused q|k|v projection: per-head RMS norm of q and k (weights shared by the heads), queries times
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)``, keys (``d`` wide) and values (``dv`` wide) into their pages."""
+    _need_cuda(qkv, q_out, positions, slot_mapping, k_cache, v_cache)
+    T = qkv.shape[0]
+    assert qkv.shape[1] == ((H + K) * d + K * dv if write_kv else H * d) and tuple(q_out.shape) == (T, H * d)
+    page_size = k_cache.shape[2]
+    _cost(_size(qkv) * 2)
+    _check(_lib("mb_attention_sigmoid").mb_qkv_heads_sigmoid(
+        _ptr(qkv), _code(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(positions), _c_float(temp_coef),
+        _c_int(temp_every), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(dv),
+        _c_int(page_size), _c_int(int(write_kv)), _stream()), "q|k|v heads (sigmoid attention)")
+
+
+def attention_sigmoid(q, k_cache, v_cache, out, ctx, block_table, bias: torch.Tensor, H: int, K: int, d: int, dv: int, scale: float) -> None:
+    """``out_i = sum_{j <= i} sigmoid(q_i . k_j * scale + bias[head, min(i - j, span - 1)]) v_j`` over the paged cache; ``bias``
+    float32 ``[H, span]``."""
+    _need_cuda(q, k_cache, v_cache, out, block_table, bias)
+    T = q.shape[0]
+    page_size = k_cache.shape[2]
+    assert tuple(q.shape) == (T, H * d) and tuple(out.shape) == (T, H * dv) and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+    assert bias.dtype == torch.float32 and bias.shape[0] == H and k_cache.shape[3] == d and v_cache.shape[3] == dv
+    if T == 0:
+        return
+    if launch_log is not None:
+        size = q.element_size()
+        _cost(T * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+        _pending_cost["rows"] = "all"
+    _check(_lib("mb_attention_sigmoid").mb_attention_sigmoid(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
+        _ptr(ctx.positions), _ptr(bias), _c_int(bias.shape[1]), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size),
+        _c_float(scale), _stream()), "attention (sigmoid)")
+
+
+def library_jobs(*names: str) -> dict:
+    """``{library: (sources, defines)}`` for libraries of the package that a part wants compiled before its model first runs."""
+    return {n: (build.LIBRARIES[n], []) for n in names}
+
+
+def sigmoid_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
+    """The kernels a sigmoid-attention mixer of this head layout runs."""
+    return library_jobs("mb_attention_sigmoid")

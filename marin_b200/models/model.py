@@ -121,7 +121,7 @@ class Model:
         T = ctx.num_tokens
         hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
         ops.stage_name = "embedding"
-        self.embedding.forward(ctx.token_ids, hidden)
+        self.embedding.forward(ctx.token_ids, hidden, ctx.positions)
         if observe is not None:
             observe(0, hidden)
         carried = None            # the next block's first norm, if the block before could carry it on its last product

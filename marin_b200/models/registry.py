@@ -19,6 +19,8 @@ class Architecture:
     model_type: str
     config_class: type
     build_spec: Callable[[ModelConfig], ModelSpec]
+    #: optional: ``resolve_shapes(config, {tensor name: shape})`` takes sizes that only a checkpoint's tensors give
+    resolve_shapes: Optional[Callable[[ModelConfig, Dict[str, tuple]], ModelConfig]] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}
@@ -26,23 +28,26 @@ _BY_MODEL_TYPE: Dict[str, Architecture] = {}
 
 
 def register_architecture(name: str, model_type: str, config_class: type,
-                          build_spec: Callable[[ModelConfig], ModelSpec]) -> Architecture:
-    arch = Architecture(name, model_type, config_class, build_spec)
+                          build_spec: Callable[[ModelConfig], ModelSpec], resolve_shapes=None) -> Architecture:
+    arch = Architecture(name, model_type, config_class, build_spec, resolve_shapes)
     _BY_NAME[name] = arch
     _BY_MODEL_TYPE[model_type] = arch
     return arch
 
 
 def architecture_for(raw: Dict[str, Any]) -> Architecture:
-    """The registered architecture a raw config.json names."""
-    for name in raw.get("architectures") or []:
+    """The registered architecture a raw config.json names (``architectures``, a single ``architecture``, or ``model_type``)."""
+    named = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):
+        named.append(raw["architecture"])
+    for name in named:
         if name in _BY_NAME:
             return _BY_NAME[name]
     model_type: Optional[str] = raw.get("model_type")
     if model_type in _BY_MODEL_TYPE:
         return _BY_MODEL_TYPE[model_type]
     raise ConfigError(
-        f"config.json names architectures {raw.get('architectures')!r} / model_type {model_type!r}; "
+        f"config.json names architectures {named!r} / model_type {model_type!r}; "
         f"registered: {sorted(_BY_NAME)}"
     )
 

@@ -1,5 +1,5 @@
 """The parts models are put together from, and the registries that name them."""
-from . import block, embedding, feedforward, mixer, norm, position  # noqa: F401  (registration)
+from . import block, embedding, feedforward, mixer, norm, position, recurrent  # noqa: F401  (registration)
 from .base import Part, Runtime
 from .mixer import Mixer, PagedKV, StateNeed
 from .feedforward import FeedForward

@@ -37,11 +37,11 @@ def element_size(dtype: torch.dtype) -> int:
 
 def spec_bytes(spec: TensorSpec, dtype: torch.dtype) -> int:
     """Bytes of one tensor as it is kept on the device: matrices and tables in the runtime's dtype, norm weights
-    in float32, integer tables in int32."""
+    and other small vectors in float32, integer tables in int32."""
     count = 1
     for s in spec.shape:
         count *= int(s)
-    return count * (4 if spec.role in ("norm", "int_table") else element_size(dtype))
+    return count * (4 if spec.role in ("norm", "bias", "int_table") else element_size(dtype))
 
 
 class Part:

@@ -14,19 +14,22 @@ from .spec import LayerSpec, TensorSpec
 @register_block("prenorm")
 class PreNormBlock(Part):
     """``h += mixer(norm1(h)); h += feedforward(norm2(h))`` — the residual stream ``h`` stays
-    float32 and both parts add into it (crates/model/src/qwen3/layer.rs:56-103)."""
+    float32 and both parts add into it (crates/model/src/qwen3/layer.rs:56-103).  A layer whose spec has no
+    feed-forward has the first sublayer only (and no second norm)."""
 
     def __init__(self, spec: LayerSpec):
         names = spec.names
         norm_cls = lookup("norm", spec.norm.kind)
         self.norm1 = norm_cls(name=f"{spec.prefix}.{names['norm1']}", **spec.norm.params)
-        self.norm2 = norm_cls(name=f"{spec.prefix}.{names['norm2']}", **spec.norm.params)
         self.mixer = lookup("mixer", spec.mixer.kind)(name=f"{spec.prefix}.{names['mixer']}", **spec.mixer.params)
-        self.feedforward = lookup("feedforward", spec.feedforward.kind)(
-            name=f"{spec.prefix}.{names['feedforward']}", **spec.feedforward.params)
+        self.norm2 = self.feedforward = None
+        if spec.feedforward is not None:
+            self.norm2 = norm_cls(name=f"{spec.prefix}.{names['norm2']}", **spec.norm.params)
+            self.feedforward = lookup("feedforward", spec.feedforward.kind)(
+                name=f"{spec.prefix}.{names['feedforward']}", **spec.feedforward.params)
 
     def parts(self) -> List[Part]:
-        return [self.norm1, self.mixer, self.norm2, self.feedforward]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feedforward) if p is not None]
 
     def tensor_specs(self) -> List[TensorSpec]:
         return [s for p in self.parts() for s in p.tensor_specs()]
@@ -69,6 +72,14 @@ class PreNormBlock(Part):
         if x_in is None:
             ops.stage_name = "norm"
         x = x_in if x_in is not None else self.norm1.forward(hidden, normed)
+        if self.feedforward is None:
+            rider = None
+            if next_block is not None and getattr(next_block, "chains_norm", False):
+                rider = self._rider(next_block.norm1, self.mixer, next_block.mixer, normed)
+            if rider is not None:
+                return self.mixer.forward(x, ctx, cache, hidden, then_norm=rider)
+            self.mixer.forward(x, ctx, cache, hidden)
+            return None
         rider = self._rider(self.norm2, self.mixer, self.feedforward, normed)
         x = self.mixer.forward(x, ctx, cache, hidden, then_norm=rider) if rider is not None else self.mixer.forward(x, ctx, cache, hidden)
         if x is None:

@@ -73,3 +73,37 @@ class SwiGLU(FeedForward):
             ops.swiglu(gate_up, act)
         ops.stage_name = "down"
         return ops.gemm(act, self.w_down, residual, accumulate=True, then_norm=then_norm)
+
+
+@register_feedforward("polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """``down( act( x W_up^T ) )`` with ``act = a N(z) + b N(z^2) + c N(z^3) + e``: powers element by element, ``N`` a token's
+    row divided by its root mean square (``eps`` under the root), the four numbers learned (tensor ``<name>.<act>``).  The
+    sums run in float32; in bfloat16 mode the up projection is kept in float32 for them."""
+
+    def __init__(self, hidden: int, intermediate: int, name: str, eps: float, names=("up", "down", "act")):
+        self.hidden, self.intermediate, self.name, self.eps = int(hidden), int(intermediate), name, float(eps)
+        self.up_name, self.down_name, self.act_name = (f"{name}.{n}" for n in names)
+        self.w_up = self.w_down = self.coef = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, i = self.hidden, self.intermediate
+        return [TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i)), TensorSpec(self.act_name, (4,), "norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_up = rt.matrix(tensors.pop(self.up_name))
+        self.w_down = rt.matrix(tensors.pop(self.down_name))
+        self.coef = rt.f32(tensors.pop(self.act_name))
+
+    def forward(self, x, ctx, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        ops.stage_name = "up"
+        z = ws.get("ffn_up", (T, self.intermediate), torch.float32)
+        ops.gemm(x, self.w_up, z)
+        ops.stage_name = "polynorm"
+        act = ws.get("ffn_act", (T, self.intermediate), x.dtype)
+        ops.polynorm(z, self.coef, self.eps, act)
+        ops.stage_name = "down"
+        ops.gemm(act, self.w_down, residual, accumulate=True)
+        return None

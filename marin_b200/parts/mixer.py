@@ -29,15 +29,21 @@ from .spec import PartSpec, TensorSpec
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of ``kv_heads`` heads of ``head_dim`` per position, kept in pages.
-    ``window`` = how many of the latest positions are ever read again (None: all)."""
+    ``window`` = how many of the latest positions are ever read again (None: all).
+    ``v_head_dim``: the size of a value head where it differs from a key head's."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim is not None else self.head_dim
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
         """Bytes one position of one layer holds in the cache (keys and values)."""
-        return 2 * self.kv_heads * self.head_dim * element_size(dtype)
+        return self.kv_heads * (self.head_dim + self.value_dim) * element_size(dtype)
 
     def bytes_read(self, context: int, dtype: torch.dtype) -> int:
         """Bytes one decoded token reads of a sequence of ``context`` positions."""
@@ -184,3 +190,113 @@ class GQAttention(Mixer):
                       self.head_dim, self.scale, self.window or 0, plans.get(self.decode_plan_key()) if plans else None)
         ops.stage_name = "o"
         return ops.gemm(out, self.w_o, residual, accumulate=True, then_norm=then_norm)
+
+
+def distance_bucket(n: int, rows: int, farthest: float) -> int:
+    """Row of a distance table of ``rows`` rows for the distance ``n >= 0``: the first half of the rows take one distance
+    each; the other half are spread evenly over the logarithm of the distance, up to ``farthest``; what lies beyond takes
+    the last row."""
+    half = rows // 2
+    if n < half:
+        return n
+    if half == 0 or farthest <= half:
+        return rows - 1
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(farthest / half) * (rows - half))))
+
+
+@register_mixer("sigmoid_attention")
+class SigmoidAttention(Mixer):
+    """Causal grouped-query attention without a softmax, over the paged cache.
+
+    ``q, k, v = x W^T`` (no bias; value heads ``v_head_dim`` wide); per-head RMS norm of q and k over ``head_dim`` (one
+    weight each, shared by the heads); no rotation.  Positions enter in two ways: queries are multiplied by
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)`` (``temp_coef = 0``: not at all), and a learned table over the
+    distance is added to the score, ``rel[distance_bucket(i - j), head]`` with ``bias_rows`` rows reaching to ``bias_max``
+    (``bias_rows = 0``: no table).  The weight of a key ``j <= i`` is ``sigmoid(q . k * scale + rel + pb[head])`` with a
+    learned number ``pb`` per head; weights are not normalised over the keys.  Output through ``o`` into the residual.
+    At load the table and ``pb`` become one float32 table ``[heads, span]`` over the distance, which the kernels index.
+    """
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "rel": "distance_bias", "pb": "head_bias"}
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, name: str, v_head_dim: Optional[int] = None,
+                 scale: Optional[float] = None, qk_norm: bool = True, norm_eps: float = 1e-6, temp_coef: float = 0.0,
+                 temp_every: int = 1, bias_rows: int = 0, bias_max: float = 0.0, head_bias: bool = True, names=None):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.heads % self.kv_heads != 0:
+            raise ValueError(f"{heads} heads cannot share {kv_heads} kv heads evenly")
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else self.head_dim
+        self.name, self.qk_norm, self.norm_eps = name, bool(qk_norm), float(norm_eps)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.temp_coef, self.temp_every = float(temp_coef), int(temp_every)
+        if self.temp_every <= 0:
+            raise ValueError("temp_every must be positive")
+        self.bias_rows, self.bias_max, self.head_bias = int(bias_rows), float(bias_max), bool(head_bias)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.q_dim, self.k_dim, self.v_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim, self.kv_heads * self.v_head_dim
+        self.w_qkv = self.w_o = self.q_weight = self.k_weight = self.bias = None
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        return PagedKV(self.kv_heads, self.head_dim, None, self.v_head_dim)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h = self.hidden
+        specs = [TensorSpec(self._n("q"), (self.q_dim, h)), TensorSpec(self._n("k"), (self.k_dim, h)),
+                 TensorSpec(self._n("v"), (self.v_dim, h)), TensorSpec(self._n("o"), (h, self.heads * self.v_head_dim))]
+        if self.qk_norm:
+            specs += [TensorSpec(self._n("q_norm"), (self.head_dim,), "norm"), TensorSpec(self._n("k_norm"), (self.head_dim,), "norm")]
+        if self.bias_rows:
+            specs.append(TensorSpec(self._n("rel"), (self.bias_rows, self.heads), "bias"))
+        if self.head_bias:
+            specs.append(TensorSpec(self._n("pb"), (self.heads,), "bias"))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        q, k, v = (tensors.pop(self._n(p)) for p in "qkv")
+        self.w_qkv = rt.matrix(torch.cat([q, k, v], dim=0))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        if self.qk_norm:
+            self.q_weight = rt.f32(tensors.pop(self._n("q_norm")))
+            self.k_weight = rt.f32(tensors.pop(self._n("k_norm")))
+        # everything added to a score as a function of head and distance, as one table over the distance: beyond
+        # bias_max every distance falls into the last row, so the table ends there
+        span = int(math.floor(self.bias_max)) + 2 if self.bias_rows else 1
+        table = torch.zeros(self.heads, span, dtype=torch.float32)
+        if self.bias_rows:
+            rel = tensors.pop(self._n("rel")).to("cpu", torch.float32)
+            rows = torch.tensor([distance_bucket(n, self.bias_rows, self.bias_max) for n in range(span)], dtype=torch.long)
+            table += rel[rows].t()
+        if self.head_bias:
+            table += tensors.pop(self._n("pb")).to("cpu", torch.float32)[:, None]
+        self.bias = table.to(rt.device).contiguous()
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + self.v_head_dim)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.sigmoid_attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim, self.v_head_dim)
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        writes = cache.owner
+        w = self.w_qkv if writes else self.w_qkv[: self.q_dim]
+        ops.stage_name = "q|k|v"
+        qkv = ws.get("qkv", (T, w.shape[0]), x.dtype)
+        ops.gemm(x, w, qkv)
+        ops.stage_name = "heads"
+        q = ws.get("q", (T, self.q_dim), x.dtype)
+        ops.qkv_heads_sigmoid(qkv, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions, self.temp_coef, self.temp_every,
+                              cache.slot_mapping, cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes)
+        out = ws.get("attn_out", (T, self.heads * self.v_head_dim), x.dtype)
+        ops.stage_name = "attention"
+        ops.attention_sigmoid(q, cache.k, cache.v, out, ctx, cache.block_table, self.bias, self.heads, self.kv_heads,
+                              self.head_dim, self.v_head_dim, self.scale)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None

@@ -38,3 +38,32 @@ class RMSNorm(Part):
     def coupling(self, out: torch.Tensor) -> "ops.NormOut":
         """This norm as a rider on the product that last updates its input (``ops.gemm(..., then_norm=...)``)."""
         return ops.NormOut(self.weight, self.unit_offset, self.eps, out)
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Part):
+    """``y_i = tanh(alpha * x_i) * w_i + b_i``: a norm that takes no statistic of the row (no mean, no variance), with one
+    learned scalar ``alpha``.  ``eps`` is accepted like every norm's and not used.  ``names`` gives the tensors' names
+    inside ``name`` (weight, bias, alpha); ``bias=False`` leaves the offset out."""
+
+    def __init__(self, dim: int, name: str, eps: float = 0.0, bias: bool = True, names=("weight", "bias", "alpha")):
+        self.dim, self.name, self.eps, self.has_bias = int(dim), name, float(eps), bool(bias)
+        join = lambda part: f"{name}.{part}" if part else name     # "" names the tensor `name` itself
+        self.weight_name, self.bias_name, self.alpha_name = (join(p) for p in names)
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [TensorSpec(self.weight_name, (self.dim,), "norm")]
+        if self.has_bias:
+            specs.append(TensorSpec(self.bias_name, (self.dim,), "bias"))
+        return specs + [TensorSpec(self.alpha_name, (), "norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.weight = rt.f32(tensors.pop(self.weight_name))
+        self.bias = rt.f32(tensors.pop(self.bias_name)) if self.has_bias else None
+        self.alpha = rt.f32(tensors.pop(self.alpha_name)).reshape(1)
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``x`` float32 ``[rows, dim]`` → ``out`` (float32 or bfloat16) ``[rows, dim]``."""
+        ops.dynamic_tanh(x, self.weight, self.bias, self.alpha, out)
+        return out

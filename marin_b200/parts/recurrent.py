@@ -1,0 +1,168 @@
+"""Mixers whose memory is a fixed-size state per request instead of a cache that grows: a matrix per head that every
+token updates (``StateNeed``), kept in float32 in the request's state slot.
+
+Both walk the tokens a request brings to a step in order, from the state the steps before left (zeros at admission), so
+a prompt may be cut anywhere and single decoded tokens take the same path.  Which tokens belong to which request and
+which slot they use is read on the device (``ctx.cu_tokens``, ``cache.slots``): single-token steps may be captured.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..kernels import ops
+from .base import Runtime
+from .mixer import Mixer, StateNeed
+from .registry import register_mixer
+from .spec import TensorSpec
+
+
+@register_mixer("linear_attention")
+class LinearAttention(Mixer):
+    """Linear attention with a fixed decay per head and an output gate.
+
+    ``q = silu(W_q x)``, ``k = silu(W_k x)`` (``heads`` x ``dim``), ``v = silu(W_v x)`` (``heads`` x ``vdim``); per head
+    ``S_t = decay_h S_(t-1) + k_t v_t^T`` and ``o_t = S_t^T q_t`` (no other scale).  The heads side by side are divided by
+    their common root mean square (``norm_eps`` under the root), times the weight ``norm``, times ``sigmoid(W_g x)``, and go
+    through ``W_o`` into the residual.  ``decay``: one number per head.
+    """
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
+
+    def __init__(self, hidden: int, heads: int, dim: int, vdim: int, decay: Sequence[float], name: str, norm_eps: float = 1e-6,
+                 names=None):
+        self.hidden, self.heads, self.dim, self.vdim = int(hidden), int(heads), int(dim), int(vdim)
+        self.decay_values = [float(d) for d in decay]
+        if len(self.decay_values) != self.heads:
+            raise ValueError(f"{len(self.decay_values)} decays for {self.heads} heads")
+        self.name, self.norm_eps = name, float(norm_eps)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.qk, self.hv = self.heads * self.dim, self.heads * self.vdim
+        self.w_in = self.w_o = self.norm_w = self.decay = None
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        return StateNeed((self.heads, self.dim, self.vdim), torch.float32)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h = self.hidden
+        return [TensorSpec(self._n("q"), (self.qk, h)), TensorSpec(self._n("k"), (self.qk, h)), TensorSpec(self._n("v"), (self.hv, h)),
+                TensorSpec(self._n("g"), (self.hv, h)), TensorSpec(self._n("o"), (h, self.hv)), TensorSpec(self._n("norm"), (self.hv,), "norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        # one matrix for the four projections of x: q | k | v | g
+        self.w_in = rt.matrix(torch.cat([tensors.pop(self._n(p)) for p in "qkvg"], dim=0))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        self.norm_w = rt.f32(tensors.pop(self._n("norm")))
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + 4.0 * tokens * self.heads * self.dim * self.vdim
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_activations", "mb_recurrent")
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        qk, hv = self.qk, self.hv
+        ops.stage_name = "q|k|v|g"
+        proj = ws.get("lin_proj", (T, 2 * qk + 2 * hv), x.dtype)
+        ops.gemm(x, self.w_in, proj)
+        ops.stage_name = "recurrence"
+        o = ws.get("lin_o", (T, hv), torch.float32)
+        ops.linear_attention_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + hv], self.decay, cache.state, ctx,
+                                  cache.slots, o, self.heads, self.dim, self.vdim)
+        ops.stage_name = "norm, gate"
+        gated = ws.get("lin_gated", (T, hv), x.dtype)
+        ops.gated_rmsnorm(o, self.norm_w, proj[:, 2 * qk + hv:], "sigmoid", self.norm_eps, gated)
+        ops.stage_name = "o"
+        ops.gemm(gated, self.w_o, residual, accumulate=True)
+        return None
+
+
+@register_mixer("wkv")
+class WKV(Mixer):
+    """Time mixing with a decay that depends on the token (RWKV-style).
+
+    With ``x'`` the row before in the sequence (zeros before the first token) each of r, k, v, g, w reads its own mix
+    ``x + (x' - x) * mu_s``.  ``r, k, v = W_r, W_k, W_v`` of their mixes (``heads`` x ``dim``), ``gate = silu(W_g mix_g)``,
+    ``decay = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))`` per head and key channel.  Per head
+    ``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t`` (the bonus ``u`` for the current token only), then
+    ``S_t = diag(decay_t) S_(t-1) + k_t v_t^T``.  Each head's ``o`` is divided by its root mean square (``norm_eps`` under the
+    root); heads side by side, times ``norm``, times the gate, through ``W_o`` into the residual.  The state of a request is
+    the matrices of all heads and the last row of ``x`` it has seen.
+    """
+
+    NAMES = {"r": "r", "k": "k", "v": "v", "g": "g", "o": "o", "w1": "w1", "w2": "w2", "w0": "w0", "u": "u", "norm": "norm",
+             "mu": "mu"}
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, hidden: int, heads: int, dim: int, decay_rank: int, name: str, norm_eps: float = 1e-6, names=None):
+        self.hidden, self.heads, self.dim, self.rank = int(hidden), int(heads), int(dim), int(decay_rank)
+        self.name, self.norm_eps = name, float(norm_eps)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.n = self.heads * self.dim
+        self.matrix_floats = self.heads * self.dim * self.dim
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        return StateNeed((self.matrix_floats + self.hidden,), torch.float32)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, n = self.hidden, self.n
+        specs = [TensorSpec(f"{self._n('mu')}.{s}", (h,), "bias") for s in self.MIXES]
+        specs += [TensorSpec(self._n(p), (n, h)) for p in "rkvg"]
+        specs += [TensorSpec(self._n("w1"), (self.rank, h)), TensorSpec(self._n("w2"), (n, self.rank)),
+                  TensorSpec(self._n("w0"), (n,), "bias"), TensorSpec(self._n("u"), (self.heads, self.dim), "bias"),
+                  TensorSpec(self._n("norm"), (n,), "norm"), TensorSpec(self._n("o"), (h, n))]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.mu = rt.f32(torch.stack([tensors.pop(f"{self._n('mu')}.{s}").to(torch.float32) for s in self.MIXES]))
+        self.w_r, self.w_k, self.w_v, self.w_g = (rt.matrix(tensors.pop(self._n(p))) for p in "rkvg")
+        self.w_1, self.w_2 = rt.matrix(tensors.pop(self._n("w1"))), rt.matrix(tensors.pop(self._n("w2")))
+        self.w0 = rt.f32(tensors.pop(self._n("w0")))
+        self.u = rt.f32(tensors.pop(self._n("u"))).reshape(-1)
+        self.norm_w = rt.f32(tensors.pop(self._n("norm")))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + 6.0 * tokens * self.heads * self.dim * self.dim
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_activations", "mb_recurrent")
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        n = self.n
+        state = cache.state[:, : self.matrix_floats]
+        carry = cache.state[:, self.matrix_floats:]
+        ops.stage_name = "token shift"
+        mixes = ws.get("wkv_mixes", (len(self.MIXES), T, self.hidden), x.dtype)
+        ops.shift_mix(x, carry, ctx, cache.slots, self.mu, mixes)
+        ops.stage_name = "r, k, v, g"
+        rkvg = ws.get("wkv_rkvg", (4, T, n), x.dtype)
+        for i, w in enumerate((self.w_r, self.w_k, self.w_v, self.w_g)):
+            ops.gemm(mixes[i], w, rkvg[i])
+        ops.stage_name = "decay"
+        low = ws.get("wkv_low", (T, self.rank), x.dtype)
+        ops.gemm(mixes[4], self.w_1, low)
+        ops.tanh_cap(low, 1.0)
+        wraw = ws.get("wkv_wraw", (T, n), torch.float32)
+        ops.gemm(low, self.w_2, wraw)
+        ops.stage_name = "recurrence"
+        out = ws.get("wkv_out", (T, n), x.dtype)
+        ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], rkvg[3], wraw, self.w0, self.u, self.norm_w, self.norm_eps, state, carry, x, ctx,
+                     cache.slots, out, self.heads, self.dim)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None

@@ -16,8 +16,9 @@ class TensorSpec:
     """One tensor a part expects in the checkpoint.
 
     ``role`` decides storage and random initialisation: ``matrix`` (bf16 or f32,
-    N(0, 0.02)), ``norm`` (kept f32 on the device, 1 + N(0, 0.05)), ``table``
-    (an embedding table, treated like a matrix), ``int_table`` (int32).
+    N(0, 0.02)), ``norm`` (kept f32 on the device, 1 + N(0, 0.05)), ``bias`` (kept f32 on
+    the device, N(0, 0.02): offsets, mixing coefficients, small tables added to scores),
+    ``table`` (an embedding table, treated like a matrix), ``int_table`` (int32).
     """
 
     name: str
@@ -40,7 +41,8 @@ class LayerSpec:
     block: str
     norm: PartSpec
     mixer: PartSpec
-    feedforward: PartSpec
+    #: None: the layer has no feed-forward sublayer (and no second norm)
+    feedforward: Optional[PartSpec]
     prefix: str
     #: names inside ``prefix`` of the sub-modules, so that parts find their tensors
     names: Dict[str, str] = field(default_factory=dict)

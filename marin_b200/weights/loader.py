@@ -86,6 +86,17 @@ class Checkpoint:
             f.close()
 
 
+def checkpoint_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+    """name → shape of every tensor of a model folder, from the files' headers ({} if the folder holds no checkpoint)."""
+    if not (os.path.exists(os.path.join(model_dir, SINGLE)) or os.path.exists(os.path.join(model_dir, INDEX))):
+        return {}
+    ckpt = Checkpoint(model_dir)
+    try:
+        return {name: tuple(ckpt.info(name).shape) for name in ckpt.names()}
+    finally:
+        ckpt.close()
+
+
 def check(ckpt: Checkpoint, expected: Iterable[TensorSpec], ignorable: Sequence[str] = (),
           extras: Optional[List[str]] = None) -> List[str]:
     """Every mismatch between the checkpoint and the expected tensors, as readable lines.  Tensors of the checkpoint

@@ -53,7 +53,7 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu",
         values = 1.0 + norm_std * values
     else:
         values = matrix_std * values
-    return values.to(dtype)
+    return values.to(torch.float32 if spec.role == "bias" else dtype)
 
 
 def random_tensors(config: ModelConfig, seed: int, dtype: torch.dtype = torch.bfloat16, device="cpu",
