@@ -912,6 +912,46 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dec
         _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R), _c_int(heads), _c_int(dim), _c_int(vdim), _stream()), "linear attention (scan)")
 
 
+#: prompt portions of a bf16 linear-attention layer run in chunks of 64 tokens on the tensor cores where the head layout allows
+use_chunked_linear_attention = True
+
+
+def linear_attention_chunked_supported(dtype, dim: int, vdim: int) -> bool:
+    return dtype == torch.bfloat16 and dim % 16 == 0 and 16 <= dim <= 128 and vdim % 32 == 0
+
+
+def _chunked_job(dim: int, vdim: int) -> tuple:
+    return (["linear_attention_chunked.cu"], [f"QK_DIM={dim}", f"V_SLICE={64 if vdim % 64 == 0 else 32}"])
+
+
+def linear_attention_jobs(dtype, dim: int, vdim: int) -> dict:
+    """The kernels a linear-attention mixer of this head layout runs: the scan (any size, both dtypes; single tokens) and,
+    where the layout allows, the chunked tensor-core kernel for prompt portions."""
+    jobs = library_jobs("mb_activations", "mb_recurrent")
+    if use_chunked_linear_attention and linear_attention_chunked_supported(dtype, dim, vdim):
+        jobs[f"mb_linear_attention_chunked_d{dim}_v{64 if vdim % 64 == 0 else 32}"] = _chunked_job(dim, vdim)
+    return jobs
+
+
+def linear_attention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx,
+                             slots: torch.Tensor, o: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+    """The same recurrence as ``linear_attention_scan``, 64 tokens at a time on the tensor cores (bf16 operands, the state
+    and the weights in float32, split into two bf16 numbers where they are operands)."""
+    _need_cuda(decay, state, o, slots)
+    T = q.shape[0]
+    stride = q.stride(0)
+    assert q.dtype == k.dtype == v.dtype == torch.bfloat16 and k.stride(0) == stride and v.stride(0) == stride
+    assert tuple(q.shape) == (T, heads * dim) and tuple(k.shape) == (T, heads * dim) and tuple(v.shape) == (T, heads * vdim)
+    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, vdim) and decay.numel() == heads
+    assert o.dtype == torch.float32 and tuple(o.shape) == (T, heads * vdim)
+    R = ctx.num_requests
+    _cost(T * heads * (2 * dim + vdim) * 2 + _size(o) + 2.0 * R * heads * dim * vdim * 4, 4.0 * T * heads * dim * vdim + 4.0 * T * 64 * heads * (dim + vdim) / 2)
+    lib = build.load(f"mb_linear_attention_chunked_d{dim}_v{64 if vdim % 64 == 0 else 32}", *_chunked_job(dim, vdim))
+    _check(lib.mb_linear_attention_chunked(
+        _c_void_p(q.data_ptr()), _c_void_p(k.data_ptr()), _c_void_p(v.data_ptr()), _c_int(stride), _ptr(decay), _ptr(state),
+        _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R), _c_int(heads), _c_int(vdim), _stream()), "linear attention (chunked)")
+
+
 def wkv_scan(r, k, v, g, wraw, w0, u, norm_w, eps: float, state: torch.Tensor, carry: torch.Tensor, h: torch.Tensor, ctx,
              slots: torch.Tensor, out: torch.Tensor, heads: int, dim: int) -> None:
     """``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(w_t) S_(t-1) + k_t v_t^T`` with ``w = exp(-exp(wraw + w0))``,
@@ -949,9 +989,44 @@ def qkv_heads_sigmoid(qkv, q_out, q_weight, k_weight, eps: float, positions, tem
         _c_int(page_size), _c_int(int(write_kv)), _stream()), "q|k|v heads (sigmoid attention)")
 
 
-def attention_sigmoid(q, k_cache, v_cache, out, ctx, block_table, bias: torch.Tensor, H: int, K: int, d: int, dv: int, scale: float) -> None:
+#: bf16 sigmoid attention goes to the tensor-core kernels where the head layout allows (False: always the plain kernel)
+use_fast_sigmoid_attention = True
+
+
+def fast_sigmoid_attention_supported(dtype, H: int, K: int, d: int, dv: int) -> bool:
+    return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 128 and 16 <= dv <= 128
+            and H % K == 0 and 1 <= H // K <= 8)
+
+
+def _sigmoid_job(d: int, dv: int, group: int) -> tuple:
+    return (["attention_sigmoid_fast.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}"])
+
+
+def _sigmoid_lib(d: int, dv: int, group: int):
+    return build.load(f"mb_attention_sigmoid_fast_d{d}_v{dv}_g{group}", *_sigmoid_job(d, dv, group))
+
+
+class SigmoidDecodePlan:
+    """How single-token sigmoid attention splits a sequence's keys over CTAs: ``split`` keys (a multiple of 64) per chunk,
+    ``chunks`` chunks cover the longest sequence.  The parts add up, so any split gives the same sum up to rounding."""
+    __slots__ = ("split", "chunks")
+
+    def __init__(self, split: int, chunks: int):
+        self.split, self.chunks = int(split), int(chunks)
+
+
+def sigmoid_decode_plan(requests: int, K: int, longest: int) -> SigmoidDecodePlan:
+    """Enough chunks for about four CTAs per SM over all requests and kv heads, none shorter than 64 keys."""
+    want = max(1, -(-4 * SM_COUNT // max(1, requests * K)))
+    split = max(64, -(-(-(-max(longest, 1) // want)) // 64) * 64)
+    return SigmoidDecodePlan(split, max(1, -(-max(longest, 1) // split)))
+
+
+def attention_sigmoid(q, k_cache, v_cache, out, ctx, block_table, bias: torch.Tensor, H: int, K: int, d: int, dv: int, scale: float,
+                      plan: Optional[SigmoidDecodePlan] = None) -> None:
     """``out_i = sum_{j <= i} sigmoid(q_i . k_j * scale + bias[head, min(i - j, span - 1)]) v_j`` over the paged cache; ``bias``
-    float32 ``[H, span]``."""
+    float32 ``[H, span]``.  The first ``ctx.num_decode`` requests bring one token each, the rest portions.  ``plan`` fixes the
+    split of the single tokens' keys (a captured graph brings it); without one it follows the step's longest sequence."""
     _need_cuda(q, k_cache, v_cache, out, block_table, bias)
     T = q.shape[0]
     page_size = k_cache.shape[2]
@@ -959,8 +1034,34 @@ def attention_sigmoid(q, k_cache, v_cache, out, ctx, block_table, bias: torch.Te
     assert bias.dtype == torch.float32 and bias.shape[0] == H and k_cache.shape[3] == d and v_cache.shape[3] == dv
     if T == 0:
         return
+    size = q.element_size()
+    span = bias.shape[1]
+    if use_fast_sigmoid_attention and fast_sigmoid_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0:
+        lib = _sigmoid_lib(d, dv, H // K)
+        max_pages = block_table.shape[1]
+        nd = ctx.num_decode
+        if nd > 0:
+            if plan is None:
+                plan = sigmoid_decode_plan(nd, K, ctx.max_seq_len)
+            part = ctx.workspace.get("sigmoid_parts", (plan.chunks, nd, H, dv), torch.float32)
+            if launch_log is not None:
+                _cost(nd * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+                _pending_cost["rows"] = "decode"
+            _check(lib.mb_attn_sigmoid_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part), _ptr(block_table),
+                                              _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size),
+                                              _c_float(scale), _ptr(bias), _c_int(span), _c_int(plan.split), _c_int(plan.chunks),
+                                              _stream()), "attention (sigmoid, decode)")
+            launches_extra(1)
+        if ctx.num_requests > nd:
+            if launch_log is not None:
+                _cost((T - nd) * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+                _pending_cost["rows"] = "prefill"
+            _check(lib.mb_attn_sigmoid_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                               _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                                               _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _ptr(bias),
+                                               _c_int(span), _stream()), "attention (sigmoid, prefill)")
+        return
     if launch_log is not None:
-        size = q.element_size()
         _cost(T * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
         _pending_cost["rows"] = "all"
     _check(_lib("mb_attention_sigmoid").mb_attention_sigmoid(
@@ -975,5 +1076,9 @@ def library_jobs(*names: str) -> dict:
 
 
 def sigmoid_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
-    """The kernels a sigmoid-attention mixer of this head layout runs."""
-    return library_jobs("mb_attention_sigmoid")
+    """The kernels a sigmoid-attention mixer of this head layout runs: the head preparation and the plain kernel, and the
+    tensor-core kernels compiled for the layout where it allows."""
+    jobs = library_jobs("mb_attention_sigmoid")
+    if use_fast_sigmoid_attention and fast_sigmoid_attention_supported(dtype, H, K, d, dv):
+        jobs[f"mb_attention_sigmoid_fast_d{d}_v{dv}_g{H // K}"] = _sigmoid_job(d, dv, H // K)
+    return jobs

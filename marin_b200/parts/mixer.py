@@ -281,6 +281,12 @@ class SigmoidAttention(Mixer):
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
         return ops.sigmoid_attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim, self.v_head_dim)
 
+    def decode_plan_key(self):
+        return ("sigmoid_attention", self.kv_heads)
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        return ops.sigmoid_decode_plan(requests, self.kv_heads, span)
+
     def forward(self, x, ctx, cache, residual: torch.Tensor):
         T = x.shape[0]
         ws = ctx.workspace
@@ -295,8 +301,9 @@ class SigmoidAttention(Mixer):
                               cache.slot_mapping, cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes)
         out = ws.get("attn_out", (T, self.heads * self.v_head_dim), x.dtype)
         ops.stage_name = "attention"
+        plans = ctx.decode_plans
         ops.attention_sigmoid(q, cache.k, cache.v, out, ctx, cache.block_table, self.bias, self.heads, self.kv_heads,
-                              self.head_dim, self.v_head_dim, self.scale)
+                              self.head_dim, self.v_head_dim, self.scale, plans.get(self.decode_plan_key()) if plans else None)
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None

@@ -64,7 +64,7 @@ class LinearAttention(Mixer):
         return super().flops(tokens, pairs) + 4.0 * tokens * self.heads * self.dim * self.vdim
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
-        return ops.library_jobs("mb_activations", "mb_recurrent")
+        return ops.linear_attention_jobs(dtype, self.dim, self.vdim)
 
     def forward(self, x, ctx, cache, residual: torch.Tensor):
         T = x.shape[0]
@@ -75,8 +75,13 @@ class LinearAttention(Mixer):
         ops.gemm(x, self.w_in, proj)
         ops.stage_name = "recurrence"
         o = ws.get("lin_o", (T, hv), torch.float32)
-        ops.linear_attention_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + hv], self.decay, cache.state, ctx,
-                                  cache.slots, o, self.heads, self.dim, self.vdim)
+        # prompt portions 64 tokens at a time on the tensor cores; single tokens (and sizes that kernel is not made for, and
+        # the 32-bit path) token by token
+        chunked = (ctx.max_query_len > 1 and ops.use_chunked_linear_attention
+                   and ops.linear_attention_chunked_supported(x.dtype, self.dim, self.vdim))
+        run = ops.linear_attention_chunked if chunked else ops.linear_attention_scan
+        run(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + hv], self.decay, cache.state, ctx, cache.slots, o,
+            self.heads, self.dim, self.vdim)
         ops.stage_name = "norm, gate"
         gated = ws.get("lin_gated", (T, hv), x.dtype)
         ops.gated_rmsnorm(o, self.norm_w, proj[:, 2 * qk + hv:], "sigmoid", self.norm_eps, gated)

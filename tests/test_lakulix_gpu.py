@@ -189,6 +189,28 @@ def test_linear_attention_alone(dtype, heads, dim, vdim):
         close(feed(mixer, harness(mixer, rt), x, cuts), want, dtype, f"cuts {cuts[:4]}")
 
 
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 32, 64), (1, 128, 128), (2, 16, 32), (1, 64, 96)])
+def test_linear_attention_in_chunks_of_64(heads, dim, vdim):
+    """Prompt portions long enough for several chunks of the tensor-core kernel, cut at, just before and just after chunk
+    edges, with single tokens (the scan kernel) in between: both kernels carry the same state.  A slow decay keeps the
+    first tokens visible to the last."""
+    from marin_b200.kernels import ops
+    from marin_b200.parts import lookup
+
+    dtype = "bfloat16"
+    rt = runtime(dtype)
+    hidden, T = 48, 200
+    decay = [0.999, 0.9][:heads]
+    assert ops.linear_attention_chunked_supported(rt.dtype, dim, vdim)
+    mixer = lookup("mixer", "linear_attention")(hidden=hidden, heads=heads, dim=dim, vdim=vdim, decay=decay, name="m", norm_eps=1e-5)
+    w = mixer_weights(mixer, dtype, 9)
+    mixer.load(dict(w), rt)
+    x = torch.randn(T, hidden, generator=torch.Generator().manual_seed(10)).to(rt.dtype)
+    want = plain.lightning(x.double(), {k: v.double() for k, v in w.items()}, "m", heads, dim, vdim, decay, 1e-5)
+    for cuts in ([200], [64, 64, 72], [63, 1, 65, 1, 70], [2, 128, 1, 1, 68], [129, 71]):
+        close(feed(mixer, harness(mixer, rt), x, cuts), want, dtype, f"cuts {cuts}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, dim, rank", [(2, 16, 8), (3, 24, 12), (1, 64, 16)])
 def test_wkv_alone(dtype, heads, dim, rank):
