@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, with their fractions of roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
+    python bench.py --arch lakulix [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
 
 The default run has the layer sizes of the Qwen3-4B layout with random bfloat16 weights, a batch of 8
 sequences and a context of 4096 positions (the last timed step reaches it).  A "step" is one decode
@@ -14,6 +15,11 @@ step.  One JSON line is printed:
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   bytes a decode step has to read (every weight once, the cache of the live requests) / its time
   points     decode at batch 1 and 64
+
+``--arch lakulix`` measures another architecture instead, beside the Qwen3 layout of the same width, depth and vocabulary:
+Lakulix layers (linear attention, sigmoid attention, time mixing, in turn; a PolyNorm feed-forward in each) at the chosen
+layout's sizes, decode at the given batch and the prompt step, each with its fraction of roofline, as one JSON line of
+its own form (``--profile``: its stage tables).  The default workload and its line are not touched by it.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else 6.65 TB/s and 1.59 PFLOP/s.
 Between timed iterations nothing is flushed: a decode step reads gigabytes of weights, far more than the
@@ -244,7 +250,7 @@ def prefill_device(engine, tokens, runs, warmup):
     return statistics.median(times)
 
 
-def profile_mode(engine, args, pk):
+def profile_mode(engine, args, pk, label=None, batches=None):
     """Where the time of a decode step (batch 1, 8 and 64) and of a 2,048-token prompt goes, stage by stage
     (marin_b200/engine/profile.py).  Text to stdout; no JSON line: nothing measured here is a throughput figure."""
     import torch
@@ -256,10 +262,12 @@ def profile_mode(engine, args, pk):
     runner, vocab = engine.runner, engine.config.vocab_size
     layers = len(engine.model.blocks)
     where = f"Qwen3-{args.model.upper()} layout, {layers} of {LAYOUTS[args.model]['num_hidden_layers']} layers, bfloat16, page {PAGE}"
+    if label is not None:
+        where = f"{label}, bfloat16, page {PAGE}"
     peaks_line = f"peaks ({pk['source']}): {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16"
     print(f"{where}; {peaks_line}; in-step times under the CUDA profiling interface (medians of 6 steps)\n")
     steps, warmup = 6, 4
-    for batch in sorted({1, 8, 64, args.batch}):
+    for batch in sorted(set(batches) if batches else {1, 8, 64, args.batch}):
         ids = [f"prof{batch}_{i}" for i in range(batch)]
         for rid in ids:
             runner.begin(rid)
@@ -288,6 +296,82 @@ def profile_mode(engine, args, pk):
     return 0
 
 
+def lakulix_layout(raw: dict, layers: int) -> dict:
+    """A Lakulix configuration at a Qwen3 layout's sizes: the same width, feed-forward width, vocabulary and attention
+    heads; linear-attention heads of 128 x 128 and time-mixing heads of 64 filling the width; the three mixers in turn."""
+    width, head = raw["hidden_size"], raw["head_dim"]
+    lin_heads = width // 128
+    mixers = [
+        {"type": "lightning", "mixer": {"heads": lin_heads, "dim": 128, "vdim": 128,
+                                        "decay": [1.0 - 2.0 ** (-(3 + 5 * i / max(1, lin_heads - 1))) for i in range(lin_heads)]}},
+        {"type": "attention", "mixer": {"heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "dim": head,
+                                        "vdim": head, "scale": head ** -0.5, "bias_max": 240, "bias_rows": 32,
+                                        "q_temp": {"coef": 0.1, "every": 1024}}},
+        {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}},
+    ]
+    return {"architecture": "Lakulix", "vocab": raw["vocab_size"], "width": width, "max_positions": 2 * CONTEXT,
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [dict(mixers[i % 3], mlp={"kind": "dense", "ff": raw["intermediate_size"]}) for i in range(layers)]}
+
+
+def lakulix_mode(args, pk) -> int:
+    """Decode and prompt throughput of Lakulix at a Qwen3 layout's sizes, and of that Qwen3 layout at the same depth, with
+    their fractions of roofline: one JSON line.  With --profile: Lakulix's stage tables."""
+    import gc
+
+    import torch
+
+    from marin_b200 import Engine
+    from marin_b200.config import LakulixConfig, Qwen3Config
+
+    layers = args.layers or 12
+    raw = dict(LAYOUTS[args.model], num_hidden_layers=layers)
+    warmup = max(3, args.warmup)
+    arms = {"lakulix": LakulixConfig.from_dict(lakulix_layout(raw, layers)), "qwen3": Qwen3Config.from_dict(raw)}
+    out = {}
+    for name, cfg in arms.items():
+        if args.profile and name != "lakulix":
+            continue
+        engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, max_batch=max(args.batch, 8),
+                        token_budget=PREFILL_TOKENS)
+        fill_cache(engine)
+        if args.profile:
+            return profile_mode(engine, args, pk, f"Lakulix at the Qwen3-{args.model.upper()} layout's sizes, {layers} layers", batches=(1, args.batch))
+        weight_bytes, prefill_flops = model_bytes_and_flops(engine, args.batch, PREFILL_TOKENS)
+        kv_tok = kv_bytes_per_token(engine)
+        clocks = ClockSampler(ClockSampler.gpu_in_use())
+        clocks.start()
+        run = decode_device(engine, args.batch, args.steps, warmup, CONTEXT)
+        prefill_ms = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
+        clock_record = clocks.stop()
+        # a layer that keeps a state reads the same bytes whatever the context; a layer that keeps keys reads them all
+        state_bytes = sum(n.bytes() for n in engine.cache.state_needs.values())
+        paged_tok = sum(len(g.entries) * g.need.bytes_per_token(engine.rt.dtype) for g in engine.cache.groups)
+        step_bytes = weight_bytes + args.batch * (run["mean_context"] * paged_tok + 2 * state_bytes)
+        achieved = step_bytes / (run["ms_per_step"] / 1e3) / 1e9
+        out[name] = {
+            "decode_tok_s": round(run["tok_s"], 1), "decode_ms_per_step": round(run["ms_per_step"], 4), "decode_launches": run["launches"],
+            "decode_hbm_gbs": round(achieved, 1), "decode_hbm_frac": round(achieved / pk["hbm_gbs"], 4),
+            "prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+            "prefill_flops_frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "weight_bytes": weight_bytes, "clocks": clock_record}
+        engine.check_device()
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+    print(json.dumps({
+        "metric": f"Lakulix beside the Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
+                  f"(context {CONTEXT}), prefill tok/s at {PREFILL_TOKENS} tokens, fractions of roofline",
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "dtype": "bf16", "higher_is_better": True,
+        "data": "synthetic (uniform random token ids, seeded random weights)", "peaks": pk,
+        "config": {"layers": layers, "width": raw["hidden_size"], "ff": raw["intermediate_size"], "vocab": raw["vocab_size"],
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": PAGE,
+                   "lakulix_layers": "lightning (heads of 128 x 128), attention (the layout's heads), wkv (heads of 64) in turn, a dense feed-forward in each",
+                   "l2": "inputs larger than L2 (weights read per step exceed 126 MB)"},
+        "lakulix": out["lakulix"], "qwen3": out["qwen3"], "impl": "ours"}))
+    return 0
+
+
 def reference_arm():
     """The reference is a Rust workspace (cargo, rustc); neither exists in this image, so it cannot be
     built or installed offline, and a pip install of its source tree has nothing to install (no Python package)."""
@@ -309,10 +393,20 @@ def main() -> int:
     ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the last timed decode step reaches (default 4096)")
     ap.add_argument("--profile", action="store_true", help="print where a step's time goes, stage by stage, instead of the JSON line")
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix"],
+                    help="qwen3: the default workload; lakulix: that architecture at the layout's sizes beside the Qwen3 layout of equal size")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     CONTEXT = args.context
+    if args.arch == "lakulix":
+        if args.gpus != 1:
+            print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+            return 2
+        from marin_b200.kernels import build as _build
+
+        _build.build_all(verbose=False)
+        return lakulix_mode(args, peaks())
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -302,18 +302,23 @@ MB_API int mb_attn_sigmoid_layout(int* d, int* dv, int* group) { *d = D; *dv = D
 
 // Single tokens: requests 0 .. requests - 1 bring one token each (token t belongs to request t).  part: float32
 // [chunks][requests][K * GROUP][V_DIM]; split: keys per chunk, a multiple of 64; chunks * split covers the longest sequence.
-MB_API int mb_attn_sigmoid_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part, const int* block_table,
+MB_API int mb_attn_sigmoid_decode(const void* q, const void* k_cache, const void* v_cache, float* part, const int* block_table,
                                   int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale,
                                   const float* bias, int span, int split, int chunks, cudaStream_t s) {
     if (requests <= 0) return 0;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || split <= 0 || split % BN != 0 || chunks <= 0 || span <= 0) return MB_ERR_BAD_SIZE;
     cudaFuncSetAttribute(attn_sigmoid_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
-    int rc = launch_kernel(attn_sigmoid_decode_kernel, dim3(chunks, K, requests), 128, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
-                           (const bf16*)v_cache, part, block_table, max_pages, seq_lens, K, shift, scale, bias, span, split);
-    if (rc != 0) return rc;
-    return launch_kernel(attn_sigmoid_merge_kernel, requests * K * GROUP, DV >= 64 ? 64 : 32, 0, s, 0, (const float*)part, seq_lens, split,
-                         requests, K * GROUP, (bf16*)out);
+    return launch_kernel(attn_sigmoid_decode_kernel, dim3(chunks, K, requests), 128, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
+                         (const bf16*)v_cache, part, block_table, max_pages, seq_lens, K, shift, scale, bias, span, split);
+}
+
+// The parts of every request added in chunk order: out bf16 [requests][K * GROUP][V_DIM].
+MB_API int mb_attn_sigmoid_merge(const float* part, void* out, const int* seq_lens, int requests, int K, int split, cudaStream_t s) {
+    if (requests <= 0) return 0;
+    if (split <= 0) return MB_ERR_BAD_SIZE;
+    return launch_kernel(attn_sigmoid_merge_kernel, requests * K * GROUP, DV >= 64 ? 64 : 32, 0, s, 0, part, seq_lens, split, requests,
+                         K * GROUP, (bf16*)out);
 }
 
 // Prompt portions: requests first_req .. first_req + count - 1 of the step.

@@ -1047,11 +1047,13 @@ def attention_sigmoid(q, k_cache, v_cache, out, ctx, block_table, bias: torch.Te
             if launch_log is not None:
                 _cost(nd * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
                 _pending_cost["rows"] = "decode"
-            _check(lib.mb_attn_sigmoid_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part), _ptr(block_table),
+            _check(lib.mb_attn_sigmoid_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(part), _ptr(block_table),
                                               _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size),
                                               _c_float(scale), _ptr(bias), _c_int(span), _c_int(plan.split), _c_int(plan.chunks),
                                               _stream()), "attention (sigmoid, decode)")
-            launches_extra(1)
+            _cost(plan.chunks * nd * H * dv * 4 + nd * H * dv * size)
+            _check(lib.mb_attn_sigmoid_merge(_ptr(part), _ptr(out), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(plan.split), _stream()),
+                   "attention (sigmoid, parts added)")
         if ctx.num_requests > nd:
             if launch_log is not None:
                 _cost((T - nd) * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
