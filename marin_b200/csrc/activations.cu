@@ -36,42 +36,78 @@ MB_API int mb_dyt(const float* x, const float* w, const float* b, const float* a
 }
 
 // ---- PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e, N(y) = y / sqrt(mean(y^2) + eps) over the row ---------------------
-// One block per row; the three sums of squares (z^2, z^4, z^6) in one pass, the row read a second time for the result.
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(256) polynorm_kernel(const TI* __restrict__ z, const float* __restrict__ coef, float eps,
-                                                       TO* __restrict__ out, int n) {
+// One block of 1,024 threads per row; the three sums of squares (z^2, z^4, z^6) in one pass, the row read a second time
+// (from L2) for the result.  VEC elements per load where the row allows (16 bytes).
+template <typename TI, int VEC> struct RowLoad;
+template <> struct RowLoad<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float* v) { const float4 x = *reinterpret_cast<const float4*>(p); v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; }
+};
+template <> struct RowLoad<float, 1> { static __device__ __forceinline__ void load(const float* p, float* v) { v[0] = p[0]; } };
+template <> struct RowLoad<bf16, 1> { static __device__ __forceinline__ void load(const bf16* p, float* v) { v[0] = __bfloat162float(p[0]); } };
+template <> struct RowLoad<bf16, 4> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+};
+template <typename TO, int VEC> __device__ __forceinline__ void row_store(TO* p, const float* v) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = from_f32<TO>(v[i]);
+}
+template <> __device__ __forceinline__ void row_store<float, 4>(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+template <> __device__ __forceinline__ void row_store<bf16, 4>(bf16* p, const float* v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = packed;
+}
+
+template <typename TI, typename TO, int VEC>
+__global__ void __launch_bounds__(1024) polynorm_kernel(const TI* __restrict__ z, const float* __restrict__ coef, float eps,
+                                                        TO* __restrict__ out, int n) {
     PDL_ENTER();
     z = pdl_fresh(z);
     __shared__ float scratch[32];
     const TI* row = z + (size_t)blockIdx.x * n;
     TO* dst = out + (size_t)blockIdx.x * n;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = to_f32(row[i]), v2 = v * v;
-        s1 += v2;
-        s2 += v2 * v2;
-        s3 += v2 * v2 * v2;
+    for (int i = threadIdx.x * VEC; i < n; i += blockDim.x * VEC) {
+        float v[VEC];
+        RowLoad<TI, VEC>::load(row + i, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { const float v2 = v[e] * v[e]; s1 += v2; s2 += v2 * v2; s3 += v2 * v2 * v2; }
     }
     s1 = block_sum(s1, scratch);
     s2 = block_sum(s2, scratch);
     s3 = block_sum(s3, scratch);
     const float r1 = coef[0] / sqrtf(s1 / (float)n + eps), r2 = coef[1] / sqrtf(s2 / (float)n + eps),
-                r3 = coef[2] / sqrtf(s3 / (float)n + eps), e = coef[3];
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = to_f32(row[i]), v2 = v * v;
-        dst[i] = from_f32<TO>(r1 * v + r2 * v2 + r3 * (v2 * v) + e);
+                r3 = coef[2] / sqrtf(s3 / (float)n + eps), e0 = coef[3];
+    for (int i = threadIdx.x * VEC; i < n; i += blockDim.x * VEC) {
+        float v[VEC];
+        RowLoad<TI, VEC>::load(row + i, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { const float v2 = v[e] * v[e]; v[e] = r1 * v[e] + r2 * v2 + r3 * (v2 * v[e]) + e0; }
+        row_store<TO, VEC>(dst + i, v);
     }
+}
+
+template <typename TI, typename TO>
+static int polynorm_launch(const void* z, const float* coef, float eps, void* out, int rows, int n, cudaStream_t s) {
+    const bool vec = n % 4 == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const int threads = n >= 4096 ? 1024 : n >= 1024 ? 256 : 128;
+    if (vec) return launch_kernel(polynorm_kernel<TI, TO, 4>, rows, threads, 0, s, 0, (const TI*)z, coef, eps, (TO*)out, n);
+    return launch_kernel(polynorm_kernel<TI, TO, 1>, rows, threads, 0, s, 0, (const TI*)z, coef, eps, (TO*)out, n);
 }
 
 MB_API int mb_polynorm(const void* z, int z_dtype, const float* coef, float eps, void* out, int out_dtype, int rows, int n,
                        cudaStream_t s) {
     if (rows <= 0 || n <= 0) return 0;
-    if (z_dtype == MB_F32 && out_dtype == MB_F32)
-        return launch_kernel(polynorm_kernel<float, float>, rows, 256, 0, s, 0, (const float*)z, coef, eps, (float*)out, n);
-    if (z_dtype == MB_F32 && out_dtype == MB_BF16)
-        return launch_kernel(polynorm_kernel<float, bf16>, rows, 256, 0, s, 0, (const float*)z, coef, eps, (bf16*)out, n);
-    if (z_dtype == MB_BF16 && out_dtype == MB_BF16)
-        return launch_kernel(polynorm_kernel<bf16, bf16>, rows, 256, 0, s, 0, (const bf16*)z, coef, eps, (bf16*)out, n);
+    if (z_dtype == MB_F32 && out_dtype == MB_F32) return polynorm_launch<float, float>(z, coef, eps, out, rows, n, s);
+    if (z_dtype == MB_F32 && out_dtype == MB_BF16) return polynorm_launch<float, bf16>(z, coef, eps, out, rows, n, s);
+    if (z_dtype == MB_BF16 && out_dtype == MB_BF16) return polynorm_launch<bf16, bf16>(z, coef, eps, out, rows, n, s);
     return MB_ERR_BAD_DTYPE;
 }
 
@@ -79,7 +115,7 @@ MB_API int mb_polynorm(const void* z, int z_dtype, const float* coef, float eps,
 // o is float32 (what a recurrence leaves); g is read with a stride (it may be a slice of a wider row); gate: 0 sigmoid,
 // 1 silu, 2 none (g may then be null).
 template <typename T>
-__global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w,
+__global__ void __launch_bounds__(1024) gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w,
                                                             const T* __restrict__ g, int g_stride, int gate, float eps,
                                                             T* __restrict__ out, int n) {
     PDL_ENTER();
@@ -106,8 +142,9 @@ MB_API int mb_gated_rmsnorm(const float* o, const float* w, const void* g, int g
                             int rows, int n, cudaStream_t s) {
     if (rows <= 0 || n <= 0) return 0;
     if (gate < 0 || gate > 2 || (gate != 2 && g == nullptr)) return MB_ERR_BAD_SIZE;
-    if (dtype == MB_F32) return launch_kernel(gated_rmsnorm_kernel<float>, rows, 256, 0, s, 0, o, w, (const float*)g, g_stride, gate, eps, (float*)out, n);
-    if (dtype == MB_BF16) return launch_kernel(gated_rmsnorm_kernel<bf16>, rows, 256, 0, s, 0, o, w, (const bf16*)g, g_stride, gate, eps, (bf16*)out, n);
+    const int threads = n >= 2048 ? 1024 : n >= 512 ? 256 : 128;         // a thread takes two or three elements of a wide row
+    if (dtype == MB_F32) return launch_kernel(gated_rmsnorm_kernel<float>, rows, threads, 0, s, 0, o, w, (const float*)g, g_stride, gate, eps, (float*)out, n);
+    if (dtype == MB_BF16) return launch_kernel(gated_rmsnorm_kernel<bf16>, rows, threads, 0, s, 0, o, w, (const bf16*)g, g_stride, gate, eps, (bf16*)out, n);
     return MB_ERR_BAD_DTYPE;
 }
 
@@ -128,7 +165,7 @@ __global__ void shift_mix_kernel(const T* __restrict__ h, const float* __restric
     const int req = req_index[t];
     const bool first = cu_tokens[req] == t;
     const float* before = carry + (size_t)state_slots[req] * state_stride;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
         const float now = to_f32(h[(size_t)t * n + i]);
         const float prev = first ? before[i] : to_f32(h[(size_t)(t - 1) * n + i]);
         const float d = prev - now;
@@ -141,12 +178,14 @@ MB_API int mb_shift_mix(const void* h, int dtype, const float* carry, long long 
                         const int* cu_tokens, const int* state_slots, const float* mu, int mixes, void* out, int tokens, int n,
                         cudaStream_t s) {
     if (tokens <= 0 || n <= 0 || mixes <= 0) return 0;
-    const int threads = n >= 1024 ? 256 : 128;
+    const int threads = 128;
+    // few tokens: a thread takes one column, so that every load of a token is in flight at once; many tokens: a block a token
+    dim3 grid(tokens, tokens >= 512 ? 1 : (n + threads - 1) / threads);
     if (dtype == MB_F32)
-        return launch_kernel(shift_mix_kernel<float>, tokens, threads, 0, s, 0, (const float*)h, carry, state_stride, req_index, cu_tokens,
+        return launch_kernel(shift_mix_kernel<float>, grid, threads, 0, s, 0, (const float*)h, carry, state_stride, req_index, cu_tokens,
                              state_slots, mu, mixes, (float*)out, tokens, n);
     if (dtype == MB_BF16)
-        return launch_kernel(shift_mix_kernel<bf16>, tokens, threads, 0, s, 0, (const bf16*)h, carry, state_stride, req_index, cu_tokens,
+        return launch_kernel(shift_mix_kernel<bf16>, grid, threads, 0, s, 0, (const bf16*)h, carry, state_stride, req_index, cu_tokens,
                              state_slots, mu, mixes, (bf16*)out, tokens, n);
     return MB_ERR_BAD_DTYPE;
 }

@@ -287,7 +287,15 @@ __global__ void attn_sigmoid_merge_kernel(const float* __restrict__ part, const 
     const int chunks = (seq_lens[r] + split - 1) / split;
     for (int i = threadIdx.x; i < DV; i += blockDim.x) {
         float a = 0.0f;
-        for (int c = 0; c < chunks; ++c) a += part[(((size_t)c * R + r) * H + h) * DV + i];
+        int c = 0;
+        for (; c + 8 <= chunks; c += 8) {                      // eight loads in flight, added in chunk order
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = part[(((size_t)(c + u) * R + r) * H + h) * DV + i];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a += x[u];
+        }
+        for (; c < chunks; ++c) a += part[(((size_t)c * R + r) * H + h) * DV + i];
         out[((size_t)r * H + h) * DV + i] = __float2bfloat16_rn(a);
     }
 }

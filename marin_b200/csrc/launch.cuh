@@ -69,6 +69,11 @@ __device__ __forceinline__ T* pdl_fresh(T* p) {
 #define PDL_ENTER_EARLY() PDL_ENTER_AT_ONCE()
 #endif
 
+// The start of a kernel in which a few CTAs walk long sequences while most of the device is free (a recurrence over a
+// prompt's tokens): the kernels behind it are NOT let in at the start, because their CTAs would fill the free SMs and
+// the walking CTAs' own SMs while they wait; they are scheduled when this kernel ends.
+#define PDL_ENTER_WALK() do { MB_TRACE_MARK(); pdl_wait(); } while (0)
+
 static inline bool pdl_enabled() {
     static int state = -1;
     if (state < 0) {

@@ -36,7 +36,9 @@ static_assert(V_SLICE == 32 || V_SLICE == 64, "a CTA takes 32 or 64 value channe
 #define NT (VS / 8)
 #define LC_SMEM ((2 * CH * LDQ + 3 * CH * LDS + 2 * DQ * LDS) * 2 + 80 * 4)
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// z / (1 + e^-z) with the fast exponential and division: the result is rounded to bf16, which hides their last bits, and
+// the accurate ones were most of this kernel's instructions (144 activations a thread and chunk)
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 
 __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
@@ -49,7 +51,7 @@ __global__ void __launch_bounds__(128) linear_attention_chunked_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, int row_stride,
     const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ cu_tokens,
     const int* __restrict__ state_slots, float* __restrict__ o, int heads, int vdim) {
-    PDL_ENTER();
+    PDL_ENTER_WALK();
     q = pdl_fresh(q); k = pdl_fresh(k); v = pdl_fresh(v);
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);     // [CH][LDQ]
@@ -103,39 +105,58 @@ __global__ void __launch_bounds__(128) linear_attention_chunked_kernel(
                 }
             }
         }
-        // the chunk's q and k (activated), rows past the request's tokens zero
-        for (int idx = threadIdx.x; idx < CH * (DQ / 8) * 2; idx += 128) {
-            const int which = idx / (CH * (DQ / 8)), rest = idx % (CH * (DQ / 8));
-            const int row = rest / (DQ / 8), c = rest % (DQ / 8);
-            uint4 packed = make_uint4(0, 0, 0, 0);
-            if (row < rows) {
-                const bf16* src = (which ? k : q) + (size_t)(first + c0 + row) * row_stride + (size_t)head * DQ + c * 8;
-                const uint4 raw = *reinterpret_cast<const uint4*>(src);
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        // the chunk's q and k (activated), rows past the request's tokens zero; eight loads of a thread in flight at a time
+        constexpr int QK_ITERS = CH * (DQ / 8) * 2 / 128, QK_BATCH = QK_ITERS % 8 == 0 ? 8 : (QK_ITERS % 4 == 0 ? 4 : 2);
+        static_assert(CH * (DQ / 8) * 2 % 128 == 0 && QK_ITERS % QK_BATCH == 0, "q and k vectors divide evenly over the threads");
+#pragma unroll
+        for (int b0 = 0; b0 < QK_ITERS; b0 += QK_BATCH) {
+            uint4 raw[QK_BATCH];
+#pragma unroll
+            for (int u = 0; u < QK_BATCH; ++u) {
+                const int idx = threadIdx.x + (b0 + u) * 128;
+                const int which = idx / (CH * (DQ / 8)), rest = idx % (CH * (DQ / 8));
+                const int row = rest / (DQ / 8), c = rest % (DQ / 8);
+                raw[u] = make_uint4(0, 0, 0, 0);
+                if (row < rows) raw[u] = *reinterpret_cast<const uint4*>((which ? k : q) + (size_t)(first + c0 + row) * row_stride + (size_t)head * DQ + c * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < QK_BATCH; ++u) {
+                const int idx = threadIdx.x + (b0 + u) * 128;
+                const int which = idx / (CH * (DQ / 8)), rest = idx % (CH * (DQ / 8));
+                const int row = rest / (DQ / 8), c = rest % (DQ / 8);
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+                uint4 packed;
                 uint32_t* p = reinterpret_cast<uint32_t*>(&packed);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); p[i] = pack_bf16(silu_f(f.x), silu_f(f.y)); }
+                *reinterpret_cast<uint4*>((which ? sK : sQ) + row * LDQ + c * 8) = packed;       // silu(0) = 0: padded rows stay zero
             }
-            *reinterpret_cast<uint4*>((which ? sK : sQ) + row * LDQ + c * 8) = packed;
         }
         // v (activated) and v times lam^(rows - 1 - row) as two bf16 operands
-        for (int idx = threadIdx.x; idx < CH * (VS / 8); idx += 128) {
-            const int row = idx / (VS / 8), c = idx % (VS / 8);
-            uint4 pv = make_uint4(0, 0, 0, 0), ph = pv, pl = pv;
-            if (row < rows) {
-                const bf16* src = v + (size_t)(first + c0 + row) * row_stride + (size_t)head * vdim + vs0 + c * 8;
-                const uint4 raw = *reinterpret_cast<const uint4*>(src);
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                const float f = pw[rows - 1 - row];
-                uint32_t *a = reinterpret_cast<uint32_t*>(&pv), *b = reinterpret_cast<uint32_t*>(&ph), *cc = reinterpret_cast<uint32_t*>(&pl);
+        constexpr int V_ITERS = CH * (VS / 8) / 128;
+        uint4 vraw[V_ITERS];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 z = __bfloat1622float2(h2[i]);
-                    const __nv_bfloat162 act = __floats2bfloat162_rn(silu_f(z.x), silu_f(z.y));
-                    a[i] = *reinterpret_cast<const uint32_t*>(&act);
-                    const float2 back = __bfloat1622float2(act);     // the decayed value of the operand the other products see
-                    split_bf16(back.x * f, back.y * f, b[i], cc[i]);
-                }
+        for (int u = 0; u < V_ITERS; ++u) {
+            const int idx = threadIdx.x + u * 128;
+            const int row = idx / (VS / 8), c = idx % (VS / 8);
+            vraw[u] = make_uint4(0, 0, 0, 0);
+            if (row < rows) vraw[u] = *reinterpret_cast<const uint4*>(v + (size_t)(first + c0 + row) * row_stride + (size_t)head * vdim + vs0 + c * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < V_ITERS; ++u) {
+            const int idx = threadIdx.x + u * 128;
+            const int row = idx / (VS / 8), c = idx % (VS / 8);
+            uint4 pv, ph, pl;
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+            const float f = row < rows ? pw[rows - 1 - row] : 0.0f;
+            uint32_t *a = reinterpret_cast<uint32_t*>(&pv), *b = reinterpret_cast<uint32_t*>(&ph), *cc = reinterpret_cast<uint32_t*>(&pl);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 z = __bfloat1622float2(h2[i]);
+                const __nv_bfloat162 act = __floats2bfloat162_rn(silu_f(z.x), silu_f(z.y));
+                a[i] = *reinterpret_cast<const uint32_t*>(&act);
+                const float2 back = __bfloat1622float2(act);     // the decayed value of the operand the other products see
+                split_bf16(back.x * f, back.y * f, b[i], cc[i]);
             }
             *reinterpret_cast<uint4*>(sV + row * LDS + c * 8) = pv;
             *reinterpret_cast<uint4*>(sVh + row * LDS + c * 8) = ph;

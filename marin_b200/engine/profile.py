@@ -55,7 +55,8 @@ def lengths_of(runner: Runner, entries: Sequence[StepEntry]):
 
 def _kernel_events(prof) -> List:
     events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
-              and not e.name.lower().startswith(("memcpy", "memset"))]
+              and not e.name.lower().startswith(("memcpy", "memset"))
+              and "at::native" not in e.name]                  # torch's own kernels (a state slot zeroed at admission) are not a step's
     events.sort(key=lambda e: e.time_range.end)
     return events
 

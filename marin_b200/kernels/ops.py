@@ -920,8 +920,14 @@ def linear_attention_chunked_supported(dtype, dim: int, vdim: int) -> bool:
     return dtype == torch.bfloat16 and dim % 16 == 0 and 16 <= dim <= 128 and vdim % 32 == 0
 
 
+def _chunked_slice(vdim: int) -> int:
+    """Value channels a CTA of the chunked kernel takes.  32: twice the CTAs for a head (each repeats the small q k^T product);
+    a request's tokens are walked in order by one CTA per head and slice, so more, lighter CTAs fill more of the device."""
+    return 32
+
+
 def _chunked_job(dim: int, vdim: int) -> tuple:
-    return (["linear_attention_chunked.cu"], [f"QK_DIM={dim}", f"V_SLICE={64 if vdim % 64 == 0 else 32}"])
+    return (["linear_attention_chunked.cu"], [f"QK_DIM={dim}", f"V_SLICE={_chunked_slice(vdim)}"])
 
 
 def linear_attention_jobs(dtype, dim: int, vdim: int) -> dict:
@@ -929,7 +935,7 @@ def linear_attention_jobs(dtype, dim: int, vdim: int) -> dict:
     where the layout allows, the chunked tensor-core kernel for prompt portions."""
     jobs = library_jobs("mb_activations", "mb_recurrent")
     if use_chunked_linear_attention and linear_attention_chunked_supported(dtype, dim, vdim):
-        jobs[f"mb_linear_attention_chunked_d{dim}_v{64 if vdim % 64 == 0 else 32}"] = _chunked_job(dim, vdim)
+        jobs[f"mb_linear_attention_chunked_d{dim}_v{_chunked_slice(vdim)}"] = _chunked_job(dim, vdim)
     return jobs
 
 
@@ -946,30 +952,42 @@ def linear_attention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     assert o.dtype == torch.float32 and tuple(o.shape) == (T, heads * vdim)
     R = ctx.num_requests
     _cost(T * heads * (2 * dim + vdim) * 2 + _size(o) + 2.0 * R * heads * dim * vdim * 4, 4.0 * T * heads * dim * vdim + 4.0 * T * 64 * heads * (dim + vdim) / 2)
-    lib = build.load(f"mb_linear_attention_chunked_d{dim}_v{64 if vdim % 64 == 0 else 32}", *_chunked_job(dim, vdim))
+    lib = build.load(f"mb_linear_attention_chunked_d{dim}_v{_chunked_slice(vdim)}", *_chunked_job(dim, vdim))
     _check(lib.mb_linear_attention_chunked(
         _c_void_p(q.data_ptr()), _c_void_p(k.data_ptr()), _c_void_p(v.data_ptr()), _c_int(stride), _ptr(decay), _ptr(state),
         _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R), _c_int(heads), _c_int(vdim), _stream()), "linear attention (chunked)")
 
 
-def wkv_scan(r, k, v, g, wraw, w0, u, norm_w, eps: float, state: torch.Tensor, carry: torch.Tensor, h: torch.Tensor, ctx,
-             slots: torch.Tensor, out: torch.Tensor, heads: int, dim: int) -> None:
-    """``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(w_t) S_(t-1) + k_t v_t^T`` with ``w = exp(-exp(wraw + w0))``,
-    each head's ``o`` divided by its root mean square, times ``norm_w``, times ``silu(g)``.  ``state`` and ``carry`` are column
-    slices of one float32 state tensor (``[slots, heads * dim * dim]`` and ``[slots, width]``); the last row of ``h`` of every
-    request goes to ``carry``."""
-    _need_cuda(r, k, v, g, wraw, w0, u, norm_w, h, out, slots)
+def wkv_scan(r, k, v, wraw, w0, u, state: torch.Tensor, carry: torch.Tensor, h: torch.Tensor, ctx, slots: torch.Tensor,
+             o: torch.Tensor, heads: int, dim: int) -> None:
+    """``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(w_t) S_(t-1) + k_t v_t^T`` with ``w = exp(-exp(wraw + w0))``; ``o``
+    float32 ``[T, heads * dim]`` before its norm (``head_norm_gate``).  ``state`` and ``carry`` are column slices of one float32
+    state tensor (``[slots, heads * dim * dim]`` and ``[slots, width]``); the last row of ``h`` of every request goes to ``carry``."""
+    _need_cuda(r, k, v, wraw, w0, u, h, o, slots)
     T, n = r.shape
-    assert n == heads * dim and all(tuple(x.shape) == (T, n) and x.dtype == r.dtype for x in (k, v, g, out))
-    assert wraw.dtype == torch.float32 and tuple(wraw.shape) == (T, n) and all(x.dtype == torch.float32 and x.numel() == n for x in (w0, u, norm_w))
+    assert n == heads * dim and all(tuple(x.shape) == (T, n) and x.dtype == r.dtype for x in (k, v))
+    assert wraw.dtype == torch.float32 and tuple(wraw.shape) == (T, n) and all(x.dtype == torch.float32 and x.numel() == n for x in (w0, u))
+    assert o.dtype == torch.float32 and tuple(o.shape) == (T, n)
     assert state.dtype == torch.float32 and carry.dtype == torch.float32 and state.stride(0) == carry.stride(0)
     assert state.shape[1] == heads * dim * dim and carry.shape[1] == h.shape[1] and h.dtype == r.dtype and h.shape[0] == T
     R = ctx.num_requests
-    _cost(5 * _size(r) + _size(wraw) + 2.0 * R * heads * dim * dim * 4, 6.0 * T * heads * dim * dim)
+    _cost(3 * _size(r) + _size(wraw) + _size(o) + 2.0 * R * heads * dim * dim * 4, 6.0 * T * heads * dim * dim)
     _check(_lib("mb_recurrent").mb_wkv_scan(
-        _ptr(r), _ptr(k), _ptr(v), _ptr(g), _code(r), _ptr(wraw), _ptr(w0), _ptr(u), _ptr(norm_w), _c_float(eps),
-        _c_void_p(state.data_ptr()), _c_void_p(carry.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(h), _c_int(h.shape[1]),
-        _ptr(ctx.cu_tokens), _ptr(slots), _ptr(out), _c_int(R), _c_int(heads), _c_int(dim), _stream()), "wkv (scan)")
+        _ptr(r), _ptr(k), _ptr(v), _code(r), _ptr(wraw), _ptr(w0), _ptr(u), _c_void_p(state.data_ptr()), _c_void_p(carry.data_ptr()),
+        ctypes.c_longlong(state.stride(0)), _ptr(h), _c_int(h.shape[1]), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R),
+        _c_int(heads), _c_int(dim), _stream()), "wkv (scan)")
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, g: torch.Tensor, eps: float, out: torch.Tensor, heads: int, dim: int) -> None:
+    """Each head's ``o`` divided by its own root mean square (``eps`` under the root), times ``weight`` (float32 ``[heads * dim]``),
+    times ``silu(g)``; ``o`` float32 ``[T, heads * dim]``, ``g`` and ``out`` in the activation dtype."""
+    _need_cuda(o, weight, g, out)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and tuple(o.shape) == (T, heads * dim) and g.shape == o.shape and out.shape == o.shape
+    assert g.dtype == out.dtype and weight.dtype == torch.float32 and weight.numel() == heads * dim
+    _cost(_size(o) + _size(g) + _size(out), 8.0 * o.numel())
+    _check(_lib("mb_recurrent").mb_head_norm_gate(_ptr(o), _ptr(weight), _ptr(g), _code(g), _c_float(eps), _ptr(out), _c_int(T),
+                                                 _c_int(heads), _c_int(dim), _stream()), "head norm, gate")
 
 
 # ---- attention with sigmoid weights (csrc/attention_sigmoid.cu) ---------------------------------------------------------

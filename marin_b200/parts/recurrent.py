@@ -165,9 +165,11 @@ class WKV(Mixer):
         wraw = ws.get("wkv_wraw", (T, n), torch.float32)
         ops.gemm(low, self.w_2, wraw)
         ops.stage_name = "recurrence"
+        o = ws.get("wkv_o", (T, n), torch.float32)
+        ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], wraw, self.w0, self.u, state, carry, x, ctx, cache.slots, o, self.heads, self.dim)
+        ops.stage_name = "norm, gate"
         out = ws.get("wkv_out", (T, n), x.dtype)
-        ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], rkvg[3], wraw, self.w0, self.u, self.norm_w, self.norm_eps, state, carry, x, ctx,
-                     cache.slots, out, self.heads, self.dim)
+        ops.head_norm_gate(o, self.norm_w, rkvg[3], self.norm_eps, out, self.heads, self.dim)
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None
