@@ -372,14 +372,24 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
     for (int i = 0; i < PER; ++i) { S[i] = live ? st[(size_t)i * dim] : 0.0f; U[i] = u[(size_t)head * dim + i_lo + i]; }
     const int nthreads = blockDim.x;
     const size_t n_all = (size_t)heads * dim;
-    const int e = threadIdx.x, which = e / dim, ei = e % dim;      // this thread's element of r|k|wraw (3 dim <= the block)
-    const float w_off = (e < 3 * dim && which == 2) ? w0[(size_t)head * dim + ei] : 0.0f;
+    // this thread's elements of a token's r|k|wraw: e = thread, thread + block, ... < 3 dim
+    constexpr int NF = (3 * dim + NP * cols - 1) / (NP * cols);
+    float w_off[NF];
+#pragma unroll
+    for (int f = 0; f < NF; ++f) {
+        const int e = threadIdx.x + f * NP * cols;
+        w_off[f] = (e >= 2 * dim && e < 3 * dim) ? w0[(size_t)head * dim + e - 2 * dim] : 0.0f;
+    }
     // a token's inputs are asked for DEPTH tokens ahead and wait in registers: the walk never stands on a load
-    float ring[DEPTH], vring[DEPTH];
+    float ring[DEPTH][NF], vring[DEPTH];
 #define WKV_FETCH(slot_, n)                                                                                            \
     do {                                                                                                               \
         const size_t at_ = (size_t)(first + (n)) * n_all + (size_t)head * dim;                                         \
-        ring[slot_] = e < 3 * dim ? (which == 0 ? to_f32(rr[at_ + ei]) : which == 1 ? to_f32(kk[at_ + ei]) : wraw[at_ + ei]) : 0.0f; \
+        _Pragma("unroll") for (int f = 0; f < NF; ++f) {                                                               \
+            const int e_ = threadIdx.x + f * NP * cols;                                                                \
+            ring[slot_][f] = e_ < dim ? to_f32(rr[at_ + e_]) : e_ < 2 * dim ? to_f32(kk[at_ + e_ - dim])               \
+                                      : e_ < 3 * dim ? wraw[at_ + e_ - 2 * dim] : 0.0f;                                \
+        }                                                                                                              \
         vring[slot_] = (live && part == 0) ? to_f32(vv[at_ + j]) : 0.0f;                                               \
     } while (0)
 #pragma unroll
@@ -392,7 +402,11 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
             const int n = base + d;
             if (n >= count) break;
             float* buf = rkw[n & 1];
-            if (e < 3 * dim) buf[e] = which == 2 ? expf(-expf(ring[d] + w_off)) : ring[d];
+#pragma unroll
+            for (int f = 0; f < NF; ++f) {
+                const int e = threadIdx.x + f * NP * cols;
+                if (e < 3 * dim) buf[e] = e >= 2 * dim ? expf(-expf(ring[d][f] + w_off[f])) : ring[d][f];
+            }
             if (part == 0) vs[n & 1][col] = vring[d];
             if (n + DEPTH < count) WKV_FETCH(d, n + DEPTH);
             __syncthreads();

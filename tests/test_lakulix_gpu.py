@@ -173,7 +173,7 @@ CUTS = [[29], [13, 1, 1, 14], [2, 2, 1, 24], [1] * 29]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 16), (2, 40, 72), (1, 64, 128), (2, 16, 16)])
+@pytest.mark.parametrize("heads, dim, vdim", [(3, 8, 16), (2, 40, 72), (1, 64, 128), (2, 16, 16), (1, 128, 64), (2, 32, 32), (1, 96, 32)])
 def test_linear_attention_alone(dtype, heads, dim, vdim):
     from marin_b200.parts import lookup
 
@@ -212,7 +212,7 @@ def test_linear_attention_in_chunks_of_64(heads, dim, vdim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, dim, rank", [(2, 16, 8), (3, 24, 12), (1, 64, 16)])
+@pytest.mark.parametrize("heads, dim, rank", [(2, 16, 8), (3, 24, 12), (1, 64, 16), (1, 128, 16), (2, 32, 8), (1, 80, 8)])
 def test_wkv_alone(dtype, heads, dim, rank):
     from marin_b200.parts import lookup
 
@@ -244,7 +244,7 @@ def plain_attention(x, w, H, K, d, dv, rows, farthest, coef=0.3, every=5, scale=
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, K, d, dv, rows, farthest", [(4, 2, 16, 24, 10, 14), (2, 2, 32, 16, 7, 9.5), (4, 1, 64, 64, 16, 20),
-                                                         (6, 2, 32, 48, 12, 40), (8, 1, 16, 128, 1, 5)])
+                                                         (6, 2, 32, 48, 12, 40), (8, 1, 16, 128, 2, 5)])
 def test_sigmoid_attention_alone(dtype, H, K, d, dv, rows, farthest):
     rt = runtime(dtype)
     hidden = 40
