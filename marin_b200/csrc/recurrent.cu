@@ -348,28 +348,43 @@ __global__ void wkv_scan_kernel(const T* __restrict__ rr, const T* __restrict__ 
 }
 
 // The same with the thread's rows of the state (and of u) in registers (dim = PARTS * PER, PER a multiple of 4).
-template <typename T, int NP, int PER>
+// MODE 0: a request's tokens of the step in one walk, from its state slot and back into it.
+// A long portion is cut into blocks of `block_len` tokens that are walked side by side (the recurrence is linear in the state):
+// MODE 1: each block from a zero state, no outputs; it leaves its end state and the product of its decays per key channel in
+//         `block_state` [request * nblocks + block][head][dim][dim] and `block_decay` [..][head][dim];
+// (wkv_combine_kernel then turns the end states into the states the blocks start from: S <- W_b S + S_b, block after block)
+// MODE 2: each block again, now from its true start state in `block_state`, writing the outputs.
+template <typename T, int NP, int PER, int MODE>
 __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg_kernel(
     const T* __restrict__ rr, const T* __restrict__ kk, const T* __restrict__ vv, const float* __restrict__ wraw,
     const float* __restrict__ w0, const float* __restrict__ u, float* __restrict__ state, float* __restrict__ carry,
     long long state_stride, const T* __restrict__ h, int width, const int* __restrict__ cu_tokens,
-    const int* __restrict__ state_slots, float* __restrict__ o, int heads) {
+    const int* __restrict__ state_slots, float* __restrict__ o, int heads, float* __restrict__ block_state,
+    float* __restrict__ block_decay, int nblocks, int block_len) {
     PDL_ENTER_WALK();
+    block_state = pdl_fresh(block_state);
     rr = pdl_fresh(rr); kk = pdl_fresh(kk); vv = pdl_fresh(vv); wraw = pdl_fresh(wraw); h = pdl_fresh(h);
     constexpr int dim = NP * PER, cols = dim < 64 ? 32 : 64;      // a head's columns are split over CTAs beyond 64
     __shared__ __align__(16) float rkw[2][3 * dim];
     __shared__ float red[2][NP][cols], vs[2][cols], outs[2 * DEPTH][cols];
-    const int r = blockIdx.x, head = blockIdx.y;
+    const int r = MODE == 0 ? blockIdx.x : blockIdx.x / nblocks, blk = MODE == 0 ? 0 : blockIdx.x % nblocks, head = blockIdx.y;
     const int col = threadIdx.x % cols, part = threadIdx.x / cols, j = blockIdx.z * cols + col;
     const bool live = j < dim;
-    const int first = cu_tokens[r], count = cu_tokens[r + 1] - first;
-    if (count <= 0) return;
+    const int all_first = cu_tokens[r], all_count = cu_tokens[r + 1] - all_first;
+    const int skip = MODE == 0 ? 0 : blk * block_len;
+    if (all_count - skip <= 0) return;
+    const int first = all_first + skip, count = MODE == 0 ? all_count : min(block_len, all_count - skip);
     const int i_lo = part * PER;
     const size_t slot = (size_t)state_slots[r];
-    float* st = state + slot * state_stride + ((size_t)head * dim + i_lo) * dim + (live ? j : 0);
-    float S[PER], U[PER];
+    float* st = MODE == 0 ? state + slot * state_stride + ((size_t)head * dim + i_lo) * dim + (live ? j : 0)
+                          : block_state + ((((size_t)r * nblocks + blk) * heads + head) * dim + i_lo) * dim + (live ? j : 0);
+    float S[PER], U[PER], W[MODE == 1 ? PER : 1];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) { S[i] = live ? st[(size_t)i * dim] : 0.0f; U[i] = u[(size_t)head * dim + i_lo + i]; }
+    for (int i = 0; i < PER; ++i) {
+        S[i] = (live && MODE != 1) ? st[(size_t)i * dim] : 0.0f;
+        U[i] = u[(size_t)head * dim + i_lo + i];
+        if (MODE == 1) W[i] = 1.0f;
+    }
     const int nthreads = blockDim.x;
     const size_t n_all = (size_t)heads * dim;
     // this thread's elements of a token's r|k|wraw: e = thread, thread + block, ... < 3 dim
@@ -410,7 +425,7 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
             if (part == 0) vs[n & 1][col] = vring[d];
             if (n + DEPTH < count) WKV_FETCH(d, n + DEPTH);
             __syncthreads();
-            if (n > 0 && part == 0) {                          // the token before: the parts of its column in part order
+            if (MODE != 1 && n > 0 && part == 0) {             // the token before: the parts of its column in part order
                 const float (*p)[cols] = red[(n - 1) & 1];
                 float sum = p[0][col];
 #pragma unroll
@@ -419,7 +434,7 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
             }
             // Outputs leave in runs of DEPTH tokens, all threads storing, instead of one store per token from a quarter of them.
             // The run written here was gathered before this token's barrier; the other half of the ring is being filled.
-            if (n > DEPTH && (n - 1) % DEPTH == 0) {
+            if (MODE != 1 && n > DEPTH && (n - 1) % DEPTH == 0) {
                 for (int i = threadIdx.x; i < DEPTH * cols; i += nthreads) {
                     const int tt = n - 1 - DEPTH + i / cols, cc = i % cols;
                     if (blockIdx.z * cols + cc < dim)
@@ -430,20 +445,43 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
             const float4* r4 = reinterpret_cast<const float4*>(buf + i_lo);
             const float4* k4 = reinterpret_cast<const float4*>(buf + dim + i_lo);
             const float4* w4 = reinterpret_cast<const float4*>(buf + 2 * dim + i_lo);
-            float acc = 0.0f;
+            if (MODE == 1) {                                   // the state and the product of the decays only
 #pragma unroll
-            for (int i = 0; i < PER / 4; ++i) {
-                const float4 ri = r4[i], ki = k4[i], wi = w4[i];
-                float kv;
-                kv = ki.x * vj; acc = fmaf(fmaf(U[4 * i], kv, S[4 * i]), ri.x, acc);         S[4 * i] = fmaf(wi.x, S[4 * i], kv);
-                kv = ki.y * vj; acc = fmaf(fmaf(U[4 * i + 1], kv, S[4 * i + 1]), ri.y, acc); S[4 * i + 1] = fmaf(wi.y, S[4 * i + 1], kv);
-                kv = ki.z * vj; acc = fmaf(fmaf(U[4 * i + 2], kv, S[4 * i + 2]), ri.z, acc); S[4 * i + 2] = fmaf(wi.z, S[4 * i + 2], kv);
-                kv = ki.w * vj; acc = fmaf(fmaf(U[4 * i + 3], kv, S[4 * i + 3]), ri.w, acc); S[4 * i + 3] = fmaf(wi.w, S[4 * i + 3], kv);
+                for (int i = 0; i < PER / 4; ++i) {
+                    const float4 ki = k4[i], wi = w4[i];
+                    S[4 * i] = fmaf(wi.x, S[4 * i], ki.x * vj);         W[4 * i] *= wi.x;
+                    S[4 * i + 1] = fmaf(wi.y, S[4 * i + 1], ki.y * vj); W[4 * i + 1] *= wi.y;
+                    S[4 * i + 2] = fmaf(wi.z, S[4 * i + 2], ki.z * vj); W[4 * i + 2] *= wi.z;
+                    S[4 * i + 3] = fmaf(wi.w, S[4 * i + 3], ki.w * vj); W[4 * i + 3] *= wi.w;
+                }
+            } else {
+                float acc = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PER / 4; ++i) {
+                    const float4 ri = r4[i], ki = k4[i], wi = w4[i];
+                    float kv;
+                    kv = ki.x * vj; acc = fmaf(fmaf(U[4 * i], kv, S[4 * i]), ri.x, acc);         S[4 * i] = fmaf(wi.x, S[4 * i], kv);
+                    kv = ki.y * vj; acc = fmaf(fmaf(U[4 * i + 1], kv, S[4 * i + 1]), ri.y, acc); S[4 * i + 1] = fmaf(wi.y, S[4 * i + 1], kv);
+                    kv = ki.z * vj; acc = fmaf(fmaf(U[4 * i + 2], kv, S[4 * i + 2]), ri.z, acc); S[4 * i + 2] = fmaf(wi.z, S[4 * i + 2], kv);
+                    kv = ki.w * vj; acc = fmaf(fmaf(U[4 * i + 3], kv, S[4 * i + 3]), ri.w, acc); S[4 * i + 3] = fmaf(wi.w, S[4 * i + 3], kv);
+                }
+                red[n & 1][part][col] = acc;
             }
-            red[n & 1][part][col] = acc;
         }
     }
 #undef WKV_FETCH
+    if (MODE == 1) {
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) st[(size_t)i * dim] = S[i];
+        }
+        if (col == 0 && blockIdx.z == 0) {
+            float* wd = block_decay + (((size_t)r * nblocks + blk) * heads + head) * dim + i_lo;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) wd[i] = W[i];
+        }
+        return;
+    }
     __syncthreads();
     if (part == 0) {
         const float (*p)[cols] = red[(count - 1) & 1];
@@ -461,6 +499,7 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
                 o[(size_t)(first + tt) * n_all + (size_t)head * dim + blockIdx.z * cols + cc] = outs[tt % (2 * DEPTH)][cc];
         }
     }
+    if (MODE != 0) return;                                 // the combine kernel has left the state and the carried row
     if (live) {
 #pragma unroll
         for (int i = 0; i < PER; ++i) st[(size_t)i * dim] = S[i];
@@ -472,14 +511,59 @@ __global__ void __launch_bounds__(NP * ((NP * PER) < 64 ? 32 : 64)) wkv_scan_reg
     }
 }
 
+// Between the two walks over blocks: per request, head and state element, block after block, the end state of a block walked
+// from zero becomes the state the block starts from, S_start(b + 1) = W_b S_start(b) + S_end(b), beginning with the request's
+// state slot and ending in it; the request's last input row goes to the carried row.  grid (requests, heads, runs of 256 elements).
+template <typename T>
+__global__ void wkv_combine_kernel(float* __restrict__ state, float* __restrict__ carry, long long state_stride, const T* __restrict__ h,
+                                   int width, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
+                                   float* __restrict__ block_state, const float* __restrict__ block_decay, int heads, int dim,
+                                   int nblocks, int block_len) {
+    PDL_ENTER();
+    block_state = pdl_fresh(block_state); block_decay = pdl_fresh(block_decay); h = pdl_fresh(h);
+    const int r = blockIdx.x, head = blockIdx.y;
+    const int first = cu_tokens[r], count = cu_tokens[r + 1] - first;
+    if (count <= 0) return;
+    const int blocks = (count + block_len - 1) / block_len;
+    const size_t slot = (size_t)state_slots[r];
+    float* st = state + slot * state_stride + (size_t)head * dim * dim;
+    for (int idx = blockIdx.z * blockDim.x + threadIdx.x; idx < dim * dim; idx += gridDim.z * blockDim.x) {
+        const int i = idx / dim;
+        float S = st[idx];
+        for (int b = 0; b < blocks; ++b) {
+            const size_t at = ((size_t)r * nblocks + b) * heads + head;
+            const float end = block_state[at * dim * dim + idx];
+            block_state[at * dim * dim + idx] = S;
+            S = fmaf(block_decay[at * dim + i], S, end);
+        }
+        st[idx] = S;
+    }
+    if (head == 0 && blockIdx.z == 0) {
+        const T* last = h + (size_t)(first + count - 1) * width;
+        float* dst = carry + slot * state_stride;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32(last[i]);
+    }
+}
+
 template <typename T>
 static int wkv_scan_reg(int dim, int requests, cudaStream_t s, const void* r, const void* k, const void* v, const float* wraw, const float* w0,
                         const float* u, float* state, float* carry, long long state_stride, const void* h, int width,
-                        const int* cu_tokens, const int* state_slots, float* o, int heads) {
+                        const int* cu_tokens, const int* state_slots, float* o, int heads, float* block_state, float* block_decay,
+                        int nblocks, int block_len) {
     const int cols = dim < 64 ? 32 : 64;
-    dim3 grid(requests, heads, (dim + cols - 1) / cols);
-#define WKV_REG(NP, P) return launch_kernel(wkv_scan_reg_kernel<T, NP, P>, grid, NP * cols, 0, s, 0, (const T*)r, (const T*)k, (const T*)v, wraw, w0, u, \
-                                            state, carry, state_stride, (const T*)h, width, cu_tokens, state_slots, o, heads)
+    const int zs = (dim + cols - 1) / cols;
+#define WKV_ARGS (const T*)r, (const T*)k, (const T*)v, wraw, w0, u, state, carry, state_stride, (const T*)h, width, cu_tokens, state_slots, o, \
+                 heads, block_state, block_decay, nblocks, block_len
+#define WKV_REG(NP, P)                                                                                                             \
+    do {                                                                                                                           \
+        if (nblocks <= 1) return launch_kernel(wkv_scan_reg_kernel<T, NP, P, 0>, dim3(requests, heads, zs), NP * cols, 0, s, 0, WKV_ARGS); \
+        int rc = launch_kernel(wkv_scan_reg_kernel<T, NP, P, 1>, dim3(requests * nblocks, heads, zs), NP * cols, 0, s, 0, WKV_ARGS);    \
+        if (rc != 0) return rc;                                                                                                    \
+        rc = launch_kernel(wkv_combine_kernel<T>, dim3(requests, heads, (dim * dim + 255) / 256), 256, 0, s, 0, state, carry, state_stride, (const T*)h, width, \
+                           cu_tokens, state_slots, block_state, (const float*)block_decay, heads, dim, nblocks, block_len);           \
+        if (rc != 0) return rc;                                                                                                    \
+        return launch_kernel(wkv_scan_reg_kernel<T, NP, P, 2>, dim3(requests * nblocks, heads, zs), NP * cols, 0, s, 0, WKV_ARGS);     \
+    } while (0)
     switch (dim) {
         case 16: WKV_REG(4, 4);
         case 32: WKV_REG(4, 8);
@@ -487,13 +571,19 @@ static int wkv_scan_reg(int dim, int requests, cudaStream_t s, const void* r, co
         case 128: WKV_REG(4, 32);
     }
 #undef WKV_REG
+#undef WKV_ARGS
     return MB_ERR_BAD_SIZE;
 }
 
+// nblocks > 1 (key sizes 16, 32, 64, 128 only): every request's tokens are cut into blocks of block_len tokens that are walked
+// side by side, in three launches; block_state: float32 [requests * nblocks][heads][dim][dim], block_decay: [..][heads][dim].
 MB_API int mb_wkv_scan(const void* r, const void* k, const void* v, int dtype, const float* wraw, const float* w0, const float* u,
                        float* state, float* carry, long long state_stride, const void* h, int width, const int* cu_tokens,
-                       const int* state_slots, float* o, int requests, int heads, int dim, cudaStream_t s) {
+                       const int* state_slots, float* o, int requests, int heads, int dim, float* block_state, float* block_decay,
+                       int nblocks, int block_len, cudaStream_t s) {
     if (requests <= 0) return 0;
+    if (nblocks > 1 && (block_state == nullptr || block_decay == nullptr || block_len <= 0 || !(dim == 16 || dim == 32 || dim == 64 || dim == 128)))
+        return MB_ERR_BAD_SIZE;
     if (heads <= 0 || dim <= 0 || dim > 256) return MB_ERR_BAD_SIZE;
     const int cols = (dim + 31) / 32 * 32;
     const int threads = PARTS * cols;
@@ -501,8 +591,8 @@ MB_API int mb_wkv_scan(const void* r, const void* k, const void* v, int dtype, c
     if (smem > 200 * 1024) return MB_ERR_BAD_SIZE;
     dim3 grid(requests, heads);
     if (dim == 16 || dim == 32 || dim == 64 || dim == 128) {       // the thread's rows of the state in registers
-        if (dtype == MB_F32) return wkv_scan_reg<float>(dim, requests, s, r, k, v, wraw, w0, u, state, carry, state_stride, h, width, cu_tokens, state_slots, o, heads);
-        if (dtype == MB_BF16) return wkv_scan_reg<bf16>(dim, requests, s, r, k, v, wraw, w0, u, state, carry, state_stride, h, width, cu_tokens, state_slots, o, heads);
+        if (dtype == MB_F32) return wkv_scan_reg<float>(dim, requests, s, r, k, v, wraw, w0, u, state, carry, state_stride, h, width, cu_tokens, state_slots, o, heads, block_state, block_decay, nblocks, block_len);
+        if (dtype == MB_BF16) return wkv_scan_reg<bf16>(dim, requests, s, r, k, v, wraw, w0, u, state, carry, state_stride, h, width, cu_tokens, state_slots, o, heads, block_state, block_decay, nblocks, block_len);
         return MB_ERR_BAD_DTYPE;
     }
     if (dtype == MB_F32) {

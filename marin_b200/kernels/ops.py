@@ -958,11 +958,23 @@ def linear_attention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
         _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R), _c_int(heads), _c_int(vdim), _stream()), "linear attention (chunked)")
 
 
+#: bf16 time mixing cuts long prompt portions into blocks of this many tokens that are walked side by side (0: never)
+WKV_BLOCK_TOKENS = 128
+#: ... when the step's longest portion has at least this many tokens
+WKV_BLOCKS_FROM = 256
+
+
 def wkv_scan(r, k, v, wraw, w0, u, state: torch.Tensor, carry: torch.Tensor, h: torch.Tensor, ctx, slots: torch.Tensor,
              o: torch.Tensor, heads: int, dim: int) -> None:
     """``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(w_t) S_(t-1) + k_t v_t^T`` with ``w = exp(-exp(wraw + w0))``; ``o``
     float32 ``[T, heads * dim]`` before its norm (``head_norm_gate``).  ``state`` and ``carry`` are column slices of one float32
-    state tensor (``[slots, heads * dim * dim]`` and ``[slots, width]``); the last row of ``h`` of every request goes to ``carry``."""
+    state tensor (``[slots, heads * dim * dim]`` and ``[slots, width]``); the last row of ``h`` of every request goes to ``carry``.
+
+    The recurrence is linear in the state, so a long portion (bfloat16 mode, key sizes 16, 32, 64, 128) is cut into blocks that
+    are walked side by side: each from a zero state for its end state and the product of its decays; a short pass turns these
+    into the states the blocks start from (``S <- W_b S + S_b``, block after block); each block again from its true start, for
+    the outputs.  Twice the arithmetic, on all of the device instead of one CTA per head.  The result differs from the single
+    walk by rounding (the sums are associated differently), which is why the 32-bit path never does it."""
     _need_cuda(r, k, v, wraw, w0, u, h, o, slots)
     T, n = r.shape
     assert n == heads * dim and all(tuple(x.shape) == (T, n) and x.dtype == r.dtype for x in (k, v))
@@ -971,11 +983,22 @@ def wkv_scan(r, k, v, wraw, w0, u, state: torch.Tensor, carry: torch.Tensor, h: 
     assert state.dtype == torch.float32 and carry.dtype == torch.float32 and state.stride(0) == carry.stride(0)
     assert state.shape[1] == heads * dim * dim and carry.shape[1] == h.shape[1] and h.dtype == r.dtype and h.shape[0] == T
     R = ctx.num_requests
-    _cost(3 * _size(r) + _size(wraw) + _size(o) + 2.0 * R * heads * dim * dim * 4, 6.0 * T * heads * dim * dim)
+    nblocks, block_state, block_decay = 1, None, None
+    if (WKV_BLOCK_TOKENS and r.dtype == torch.bfloat16 and dim in (16, 32, 64, 128) and ctx.max_query_len >= WKV_BLOCKS_FROM):
+        nblocks = -(-ctx.max_query_len // WKV_BLOCK_TOKENS)
+        block_state = ctx.workspace.get("wkv_block_state", (R * nblocks, heads, dim, dim), torch.float32)
+        block_decay = ctx.workspace.get("wkv_block_decay", (R * nblocks, heads, dim), torch.float32)
+    _cost(3 * _size(r) + _size(wraw) + _size(o) + 2.0 * R * heads * dim * dim * 4, 6.0 * T * heads * dim * dim * (2 if nblocks > 1 else 1))
     _check(_lib("mb_recurrent").mb_wkv_scan(
         _ptr(r), _ptr(k), _ptr(v), _code(r), _ptr(wraw), _ptr(w0), _ptr(u), _c_void_p(state.data_ptr()), _c_void_p(carry.data_ptr()),
         ctypes.c_longlong(state.stride(0)), _ptr(h), _c_int(h.shape[1]), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(o), _c_int(R),
-        _c_int(heads), _c_int(dim), _stream()), "wkv (scan)")
+        _c_int(heads), _c_int(dim), _ptr(block_state), _ptr(block_decay), _c_int(nblocks), _c_int(WKV_BLOCK_TOKENS or 1), _stream()),
+        "wkv (blocks: from zero)" if nblocks > 1 else "wkv (scan)")
+    if nblocks > 1:                       # three kernels were launched: the blocks from zero, the combination, the blocks again
+        launches_extra(2)
+        if launch_log is not None:
+            for what in ("wkv (blocks: start states)", "wkv (blocks: outputs)"):
+                launch_log.append({"bytes": 0.0, "flops": 0.0, "bytes_per_key": 0.0, "flops_per_pair": 0.0, "stage": stage_name, "kernel": what})
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, g: torch.Tensor, eps: float, out: torch.Tensor, heads: int, dim: int) -> None:

@@ -228,6 +228,27 @@ def test_wkv_alone(dtype, heads, dim, rank):
         close(feed(mixer, harness(mixer, rt), x, cuts), want, dtype, f"cuts {cuts[:4]}")
 
 
+@pytest.mark.parametrize("heads, dim", [(2, 64), (1, 128), (2, 32), (3, 16)])
+def test_wkv_long_portions_in_blocks_side_by_side(heads, dim):
+    """Portions long enough to be cut into blocks that are walked side by side (bfloat16), cut at and around block edges,
+    with single tokens and short portions (one walk) in between: all of them carry the same state and the same last row."""
+    from marin_b200.kernels import ops
+    from marin_b200.parts import lookup
+
+    dtype = "bfloat16"
+    rt = runtime(dtype)
+    hidden, T = 40, 700
+    mixer = lookup("mixer", "wkv")(hidden=hidden, heads=heads, dim=dim, decay_rank=8, name="m", norm_eps=1e-5)
+    w = mixer_weights(mixer, dtype, 12)
+    w["m.w0"] = (torch.rand(heads * dim, generator=torch.Generator().manual_seed(13)) * 5.0 - 4.5).to(torch.bfloat16)
+    mixer.load(dict(w), rt)
+    x = torch.randn(T, hidden, generator=torch.Generator().manual_seed(14)).to(rt.dtype)
+    want = plain.wkv(x.double(), {k: v.double() for k, v in w.items()}, "m", heads, dim, 1e-5)
+    assert ops.WKV_BLOCKS_FROM <= 256 and ops.WKV_BLOCK_TOKENS == 128
+    for cuts in ([700], [256, 444], [257, 1, 1, 441], [300, 100, 300], [383, 317]):
+        close(feed(mixer, harness(mixer, rt, ctx_len=1024), x, cuts), want, dtype, f"cuts {cuts}")
+
+
 def attention_mixer(hidden, H, K, d, dv, rows, farthest, coef=0.3, every=5, scale=0.25):
     from marin_b200.parts import lookup
 
