@@ -46,11 +46,11 @@ CONFIG_C = {
     "layers": [
         {"type": "lightning", "mlp": None, "mixer": {"heads": 2, "dim": 64, "vdim": 128, "decay": [0.9, 0.999]}},
         {"type": "attention", "mlp": {"kind": "dense", "ff": 512},
-         "mixer": {"heads": 4, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.125, "bias_max": 100, "q_temp": {"coef": 0.3, "every": 64}}},
+         "mixer": {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.11, "bias_max": 100, "q_temp": {"coef": 0.2, "every": 48}}},
         {"type": "wkv", "mlp": None, "mixer": {"heads": 4, "dim": 64}},
     ],
 }
-SHAPES_C = {"rows": 16, "rank": 16}
+SHAPES_C = {"rows": 12, "rank": 24}
 CONFIGS = {"A": (CONFIG_A, SHAPES_A), "B": (CONFIG_B, SHAPES_B), "C": (CONFIG_C, SHAPES_C)}
 PAGE = {"A": 4, "B": 8, "C": 16}
 

@@ -264,7 +264,7 @@ def plain_attention(x, w, H, K, d, dv, rows, farthest, coef=0.3, every=5, scale=
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H, K, d, dv, rows, farthest", [(4, 2, 16, 24, 10, 14), (2, 2, 32, 16, 7, 9.5), (4, 1, 64, 64, 16, 20),
+@pytest.mark.parametrize("H, K, d, dv, rows, farthest", [(4, 2, 16, 24, 10, 14), (2, 2, 32, 16, 7, 9.5), (8, 2, 64, 64, 12, 20),
                                                          (6, 2, 32, 48, 12, 40), (8, 1, 16, 128, 2, 5)])
 def test_sigmoid_attention_alone(dtype, H, K, d, dv, rows, farthest):
     rt = runtime(dtype)
