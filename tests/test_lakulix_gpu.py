@@ -457,6 +457,32 @@ def test_mixed_batches_reuse_pages_and_slots(case, graphs):
         close(again[rid], case.want[rid], case.dtype, f"{rid} mixed, second time")
 
 
+def test_a_long_portion_beside_single_tokens(case):
+    """One step that holds a portion long enough for the kernels made for long portions (chunks of 64, blocks walked side by
+    side) and, beside it, requests that bring a single token each: every request gets what it gets alone."""
+    from marin_b200.engine import StepEntry
+
+    long_id = max(case.tokens, key=lambda r: len(case.tokens[r]))
+    if len(case.tokens[long_id]) < 256:
+        pytest.skip("no request of this configuration is long enough")
+    singles = [rid for rid in ("a", "c") if rid != long_id]
+    runner = case.runner(96)
+    for rid in singles:                                     # all but the last token, alone
+        runner.begin(rid)
+        runner.step([StepEntry(rid, case.tokens[rid][:-1], [])])
+    runner.begin(long_id)
+    n = len(case.tokens[long_id])
+    entries = [StepEntry(singles[0], case.tokens[singles[0]][-1:], [0]), StepEntry(long_id, case.tokens[long_id], list(range(n))),
+               StepEntry(singles[1], case.tokens[singles[1]][-1:], [0])]
+    logits = runner.step(entries)
+    close(logits[0:1], case.want[singles[0]][-1:], case.dtype, "a single token beside a long portion")
+    close(logits[1:1 + n], case.want[long_id], case.dtype, "a long portion beside single tokens")
+    close(logits[1 + n:], case.want[singles[1]][-1:], case.dtype, "another single token beside a long portion")
+    for rid in singles + [long_id]:
+        runner.end(rid)
+    runner.cache.check()
+
+
 def test_a_batch_gives_each_request_what_it_gets_alone(case):
     """float32: the logits of a request are the same bits whatever else the step holds and however its prompt was cut."""
     if case.dtype != "float32":
