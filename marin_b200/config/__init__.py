@@ -1,6 +1,7 @@
 """Typed configurations read from each architecture's own config.json keys."""
 from .base import ConfigError, ModelConfig, load_config, read_json
+from .fegarax import FegaraxConfig
 from .lakulix import LakulixConfig
 from .qwen3 import Qwen3Config
 
-__all__ = ["ConfigError", "LakulixConfig", "ModelConfig", "Qwen3Config", "load_config", "read_json"]
+__all__ = ["ConfigError", "FegaraxConfig", "LakulixConfig", "ModelConfig", "Qwen3Config", "load_config", "read_json"]

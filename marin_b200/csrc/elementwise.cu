@@ -7,29 +7,29 @@
 #include "common.cuh"
 #include "launch.cuh"
 
-// ---- embedding: out[t, :] = float(table[ids[t], :]) (+ float(pos_table[positions[t], :]) for a learned position) ------
+// ---- embedding: out[t, :] = float(table[ids[t], :]) * scale (+ float(pos_table[positions[t], :]) for a learned position) ------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, const TW* __restrict__ pos_table,
-                             const int* __restrict__ positions, float* __restrict__ out, int h) {
+                             const int* __restrict__ positions, float* __restrict__ out, int h, float scale) {
     PDL_ENTER();
     const int t = blockIdx.x;
     const TW* row = table + (size_t)ids[t] * h;
     float* dst = out + (size_t)t * h;
     if (pos_table == nullptr) {
-        for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = to_f32(row[i]);
+        for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = to_f32(row[i]) * scale;
     } else {
         const TW* prow = pos_table + (size_t)positions[t] * h;
-        for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = to_f32(row[i]) + to_f32(prow[i]);
+        for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = to_f32(row[i]) * scale + to_f32(prow[i]);
     }
 }
 
 // pos_table (same dtype as table, [positions, h]) and positions may both be null: no position term.
 MB_API int mb_embed(const int* ids, const void* table, int table_dtype, const void* pos_table, const int* positions, float* out,
-                    int tokens, int h, cudaStream_t s) {
+                    int tokens, int h, float scale, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if ((pos_table == nullptr) != (positions == nullptr)) return MB_ERR_BAD_SIZE;
-    if (table_dtype == MB_F32) return launch_kernel(embed_kernel<float>, tokens, 256, 0, s, 0, ids, (const float*)table, (const float*)pos_table, positions, out, h);
-    else if (table_dtype == MB_BF16) return launch_kernel(embed_kernel<bf16>, tokens, 256, 0, s, 0, ids, (const bf16*)table, (const bf16*)pos_table, positions, out, h);
+    if (table_dtype == MB_F32) return launch_kernel(embed_kernel<float>, tokens, 256, 0, s, 0, ids, (const float*)table, (const float*)pos_table, positions, out, h, scale);
+    else if (table_dtype == MB_BF16) return launch_kernel(embed_kernel<bf16>, tokens, 256, 0, s, 0, ids, (const bf16*)table, (const bf16*)pos_table, positions, out, h, scale);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }

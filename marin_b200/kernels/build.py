@@ -155,6 +155,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_activations": ["activations.cu"],
     "mb_recurrent": ["recurrent.cu"],
     "mb_attention_sigmoid": ["attention_sigmoid.cu"],
+    "mb_hyper": ["hyper.cu"],
+    "mb_attention_sink": ["attention_sink.cu"],
+    "mb_moe": ["moe.cu"],
     "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp", "host/safetensors.cpp"],
 }
 

@@ -110,8 +110,8 @@ def _lib(name: str):
 
 
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
-          positions: Optional[torch.Tensor] = None) -> None:
-    """``out[t] = float32(table[ids[t]])``, plus ``float32(pos_table[positions[t]])`` where a learned position table is given."""
+          positions: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """``out[t] = float32(table[ids[t]]) * scale``, plus ``float32(pos_table[positions[t]])`` where a learned position table is given."""
     _need_cuda(ids, table, out, pos_table, positions)
     T, h = out.shape
     assert ids.dtype == torch.int32 and ids.numel() == T and table.shape[1] == h and out.dtype == torch.float32
@@ -120,7 +120,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, pos_table: 
         assert pos_table.dtype == table.dtype and pos_table.shape[1] == h
     _cost(T * h * table.element_size() * (2 if pos_table is not None else 1) + _size(out) + _size(ids))
     _check(_lib("mb_elementwise").mb_embed(_ptr(ids), _ptr(table), _code(table), _ptr(pos_table), _ptr(positions if pos_table is not None else None),
-                                          _ptr(out), _c_int(T), _c_int(h), _stream()), "embed")
+                                          _ptr(out), _c_int(T), _c_int(h), _c_float(scale), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, unit_offset: bool = False) -> None:
@@ -1125,3 +1125,170 @@ def sigmoid_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
     if use_fast_sigmoid_attention and fast_sigmoid_attention_supported(dtype, H, K, d, dv):
         jobs[f"mb_attention_sigmoid_fast_d{d}_v{dv}_g{H // K}"] = _sigmoid_job(d, dv, H // K)
     return jobs
+
+
+# ---- hyper-connections: the residual kept as several streams ------------------------------------------------------------------
+def hc_step(streams: torch.Tensor, y: Optional[torch.Tensor], write=None, read=None) -> None:
+    """One pass over the residual streams (float32 ``[S, T, h]``) between two sublayers.  ``write = (mix [S, S], out [S])``:
+    ``x_t <- sum_s mix[s, t] x_s + out[t] y`` for all streams at once, ``y`` (float32 ``[T, h]``) the sublayer's output.
+    ``read = (w_in [S], norm_weight [h], eps, unit_offset, rows)``: ``rows <- rmsnorm(sum_s w_in[s] x_s)`` of the streams as
+    they are after the write, in ``rows``' dtype.  ``y`` is left zeroed for the next sublayer to add into."""
+    _need_cuda(streams, y)
+    S, T, h = streams.shape
+    assert streams.dtype == torch.float32 and (y is None or (y.dtype == torch.float32 and tuple(y.shape) == (T, h)))
+    mix = w_out = w_in = norm_w = rows = None
+    eps, unit = 0.0, False
+    if write is not None:
+        mix, w_out = write
+        assert y is not None and mix.dtype == torch.float32 and tuple(mix.shape) == (S, S) and w_out.numel() == S
+    if read is not None:
+        w_in, norm_w, eps, unit, rows = read
+        assert w_in.numel() == S and norm_w.numel() == h and tuple(rows.shape) == (T, h)
+    _cost(_size(streams) * (2 if write is not None else 1) + (_size(y) * 2 if y is not None else 0) + (_size(rows) if rows is not None else 0),
+          2.0 * T * h * S * (S + 1))
+    _check(_lib("mb_hyper").mb_hc_step(_ptr(streams), _c_int(S), _c_int(T), _c_int(h), _ptr(mix), _ptr(w_out), _ptr(y), _ptr(w_in),
+                                      _ptr(norm_w), _c_float(eps), _c_int(int(unit)), _ptr(rows),
+                                      _c_int(_code(rows) if rows is not None else F32), _stream()), "hyper-connection step")
+
+
+def hc_spread(streams: torch.Tensor) -> None:
+    """Stream 0 copied to all others."""
+    _need_cuda(streams)
+    S, T, h = streams.shape
+    assert streams.dtype == torch.float32
+    if S > 1 and T > 0:
+        _cost(_size(streams))
+        _check(_lib("mb_hyper").mb_hc_spread(_ptr(streams), _c_int(S), _c_int(T), _c_int(h), _stream()), "streams spread")
+
+
+def hc_sum(streams: torch.Tensor, rows: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out[r] = sum_s streams[s, rows[r]]`` (``rows`` None: every token in order)."""
+    _need_cuda(streams, rows, out)
+    S, T, h = streams.shape
+    count = out.shape[0]
+    assert out.dtype == torch.float32 and out.shape[1] == h and (rows is None or (rows.dtype == torch.int32 and rows.numel() == count))
+    assert rows is not None or count == T
+    _cost(count * h * 4 * (S + 1))
+    _check(_lib("mb_hyper").mb_hc_sum(_ptr(streams), _c_int(S), _c_int(T), _c_int(h), _ptr(rows), _ptr(out), _c_int(count), _stream()),
+           "streams summed")
+
+
+# ---- softmax attention with a sink, a chunked mask, values of their own width and an output gate ------------------------------
+NORM_MODES = {None: 0, "head": 1, "whole": 2}
+VALUE_MODES = {None: 0, "leave": 1, "mix": 2}
+
+
+def qkv_finish(rows: torch.Tensor, q_out: torch.Tensor, q_b, k_b, v_b, norm: Optional[str], q_w, k_w, eps: float, positions,
+               inv_freq, rot_dim: int, rot_mag: float, slot_mapping, k_cache, v_cache, value_mode: Optional[str], v_shared,
+               v_lambda, H: int, K: int, d: int, dv: int, write_kv: bool = True) -> None:
+    """Finishes the heads of a fused projection whose rows hold q | k | v (| more columns that are left alone): biases, the
+    RMS norm of q and k (``norm`` "head": per head with a weight ``[d]``; "whole": over the whole of q, and of k, with weights
+    ``[H d]`` / ``[K d]``), the rotation of the first ``rot_dim`` elements of each head (half-split pairs, sines and cosines
+    times ``rot_mag``), and the values: as they are, also left in ``v_shared`` ("leave"), or mixed with what ``v_shared`` holds,
+    ``(1 - lam) v + lam v_shared`` ("mix").  Queries go to ``q_out``, keys and values into their pages."""
+    _need_cuda(rows, q_out, q_b, k_b, v_b, q_w, k_w, positions, inv_freq, slot_mapping, k_cache, v_cache, v_shared, v_lambda)
+    T = rows.shape[0]
+    assert tuple(q_out.shape) == (T, H * d) and q_out.dtype == rows.dtype and rows.shape[1] >= ((H + K) * d + K * dv if write_kv else H * d)
+    assert k_cache.dtype == rows.dtype and v_cache.dtype == rows.dtype and k_cache.shape[3] == d and v_cache.shape[3] == dv
+    assert v_shared is None or (v_shared.dtype == rows.dtype and v_shared.numel() >= T * K * dv)
+    page_size = k_cache.shape[2]
+    _cost(2 * T * ((H + K) * d + K * dv) * rows.element_size(), 10.0 * T * (H + K) * d)
+    _check(_lib("mb_attention_sink").mb_qkv_finish(
+        _ptr(rows), _c_int(rows.shape[1]), _code(rows), _ptr(q_out), _ptr(q_b), _ptr(k_b), _ptr(v_b), _c_int(NORM_MODES[norm]), _ptr(q_w),
+        _ptr(k_w), _c_float(eps), _ptr(positions), _ptr(inv_freq), _c_int(rot_dim if inv_freq is not None else 0), _c_float(rot_mag),
+        _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(VALUE_MODES[value_mode]), _ptr(v_shared), _ptr(v_lambda), _c_int(T),
+        _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_int(int(write_kv)), _stream()), "q|k|v heads (sink attention)")
+
+
+def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d: int, dv: int, scale: float, window: int = 0,
+                   chunk: int = 0, sink: bool = True, gate: Optional[torch.Tensor] = None, plan=None) -> None:
+    """Causal softmax attention of the step's tokens over the paged cache.  A position sees the keys before it (its own
+    included), of them only the last ``window`` (0: all) and only those of its own chunk of ``chunk`` positions (0: no
+    chunks).  ``sink``: one is added to the softmax's denominator.  ``gate`` (activation dtype, a view ``[T, H dv]`` whose rows
+    may be strided): the result is multiplied by ``sigmoid(gate)``."""
+    _need_cuda(q, k_cache, v_cache, out, block_table)
+    T = q.shape[0]
+    page_size = k_cache.shape[2]
+    assert tuple(q.shape) == (T, H * d) and tuple(out.shape) == (T, H * dv) and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+    assert k_cache.shape[3] == d and v_cache.shape[3] == dv
+    gate_stride = 0
+    if gate is not None:
+        assert gate.is_cuda and gate.dtype == q.dtype and tuple(gate.shape) == (T, H * dv) and gate.stride(1) == 1
+        gate_stride = gate.stride(0)
+    if T == 0:
+        return
+    if launch_log is not None:
+        size = q.element_size()
+        _cost(T * H * (d + (3 if gate is not None else 2) * dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+        _pending_cost["rows"] = "all"
+    _check(_lib("mb_attention_sink").mb_attention_sink(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
+        _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_float(scale), _c_int(window),
+        _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _stream()), "attention (sink)")
+
+
+def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
+    return library_jobs("mb_attention_sink")
+
+
+def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span: int, window: int, chunk: int):
+    """What single-token steps fix ahead (the plain kernel needs nothing)."""
+    return None
+
+
+# ---- routed feed-forward ------------------------------------------------------------------------------------------------------
+SCORE_MODES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, experts_out: torch.Tensor, weights_out: torch.Tensor, score: str = "sigmoid",
+              renormalize: bool = False) -> None:
+    """Router logits ``x router^T`` in float32, scores by ``score``, the ``top`` best experts per token (``top`` = the outputs'
+    second size) in order of decreasing score, the lower expert among equals; their scores are the weights."""
+    _need_cuda(x, router, experts_out, weights_out)
+    T, h = x.shape
+    E, top = router.shape[0], experts_out.shape[1]
+    assert router.dtype == torch.float32 and router.shape[1] == h and experts_out.dtype == torch.int32 and weights_out.dtype == torch.float32
+    assert tuple(experts_out.shape) == (T, top) and tuple(weights_out.shape) == (T, top)
+    _cost(_size(x) + _size(router) + _size(experts_out) * 2, 2.0 * T * E * h)
+    _check(_lib("mb_moe").mb_moe_route(_ptr(x), _code(x), _ptr(router), _ptr(experts_out), _ptr(weights_out), _c_int(T), _c_int(h), _c_int(E),
+                                      _c_int(top), _c_int(SCORE_MODES[score]), _c_int(int(renormalize)), _stream()), "router")
+
+
+def moe_group(experts: torch.Tensor, E: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
+    """The (token, choice) pairs grouped by expert: ``order[offsets[e] : offsets[e + 1]]`` are expert ``e``'s pairs."""
+    _need_cuda(experts, offsets, order)
+    pairs = experts.numel()
+    assert offsets.dtype == torch.int32 and offsets.numel() >= E + 1 and order.dtype == torch.int32 and order.numel() >= pairs
+    _cost(_size(experts) * 3)
+    _check(_lib("mb_moe").mb_moe_group(_ptr(experts), _c_int(pairs), _c_int(E), _ptr(offsets), _ptr(order), _stream()), "pairs grouped")
+
+
+def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
+                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool) -> None:
+    """``y[t] += sum_c down_e( silu(gate_e x) * (up_e x) )`` over token ``t``'s chosen experts ``e`` in choice order, ``x = w h[t]``
+    where the weight goes on the input, else the result times ``w``.  Any sizes, both dtypes."""
+    _need_cuda(x, w_gate_up, w_down, experts, weights, act, y)
+    T, h = x.shape
+    top = experts.shape[1]
+    ff = w_down.shape[2]
+    assert tuple(w_gate_up.shape[1:]) == (2 * ff, h) and tuple(w_down.shape[1:]) == (h, ff) and w_gate_up.dtype == x.dtype == w_down.dtype
+    assert act.dtype == x.dtype and act.numel() >= T * top * ff and y.dtype == torch.float32 and tuple(y.shape) == (T, h)
+    pairs = T * top
+    _cost(min(pairs, w_down.shape[0]) * 3 * ff * h * x.element_size() + _size(x) + 2 * _size(y), 6.0 * pairs * ff * h)
+    _check(_lib("mb_moe").mb_moe_experts_plain(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(act),
+                                              _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(top), _c_int(int(weight_on_input)),
+                                              _stream()), "experts")
+    launches_extra(1)
+
+
+def moe_jobs(dtype, h: int, ff: int) -> dict:
+    return library_jobs("mb_moe")
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
+                y: torch.Tensor, weight_on_input: bool, workspace) -> None:
+    """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``."""
+    T, top = experts.shape
+    ff = w_down.shape[2]
+    act = workspace.get("moe_act", (T * top, ff), x.dtype)
+    moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input)

@@ -119,9 +119,22 @@ class Model:
         residual stream (float32 ``[T, hidden]``) before the first entry (i = 0) and after entry i - 1."""
         rt, ws = self.rt, ctx.workspace
         T = ctx.num_tokens
-        hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
+        S = self.spec.streams
         ops.stage_name = "embedding"
-        self.embedding.forward(ctx.token_ids, hidden, ctx.positions)
+        if S > 1:
+            # several copies of the residual stream, all equal to the embedding's output at first
+            hidden = ws.get("hidden", (S, T, self.spec.hidden_size), torch.float32)
+            self.embedding.forward(ctx.token_ids, hidden[0], ctx.positions)
+            ops.hc_spread(hidden)
+            seen, observe = observe, None
+            if seen is not None:
+                def observe(i, streams):
+                    total = torch.empty(T, self.spec.hidden_size, device=rt.device, dtype=torch.float32)
+                    ops.hc_sum(streams, None, total)
+                    seen(i, total)
+        else:
+            hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
+            self.embedding.forward(ctx.token_ids, hidden, ctx.positions)
         if observe is not None:
             observe(0, hidden)
         carried = None            # the next block's first norm, if the block before could carry it on its last product
@@ -141,7 +154,10 @@ class Model:
             return torch.empty(0, self.spec.vocab_size, device=rt.device, dtype=torch.float32)
         ops.stage_name = "final norm"
         rows = ws.get("logit_hidden", (W, self.spec.hidden_size), torch.float32)
-        ops.gather_rows(hidden, ctx.logit_rows, rows)
+        if S > 1:
+            ops.hc_sum(hidden, ctx.logit_rows, rows)
+        else:
+            ops.gather_rows(hidden, ctx.logit_rows, rows)
         normed = ws.get("logit_normed", (W, self.spec.hidden_size), rt.dtype)
         self.final_norm.forward(rows, normed)
         ops.stage_name = "head"

@@ -15,11 +15,13 @@ from .spec import TensorSpec
 class TokenEmbedding(Part):
     """``hidden[t] = float32(table[ids[t]])`` — no scaling (crates/model/src/qwen3/model.rs:133-153).  With ``positions``
     (a number of rows) a learned position table is added as it is: ``+ float32(pos_table[p])`` for the token at position
-    ``p`` of its sequence.  ``tensor`` / ``position_tensor`` name the tensors where they are not ``<name>.weight``."""
+    ``p`` of its sequence.  ``tensor`` / ``position_tensor`` name the tensors where they are not ``<name>.weight``.  ``scale``
+    multiplies the table's rows (in float32, as they enter the residual stream); a head tied to the table reads it unscaled."""
 
     def __init__(self, vocab: int, hidden: int, name: str, tensor: Optional[str] = None, positions: int = 0,
-                 position_tensor: Optional[str] = None):
+                 position_tensor: Optional[str] = None, scale: float = 1.0):
         self.vocab, self.hidden, self.name = int(vocab), int(hidden), name
+        self.scale = float(scale)
         self.tensor = tensor or f"{name}.weight"
         self.positions = int(positions)
         self.position_tensor = position_tensor or f"{name}.positions.weight"
@@ -45,9 +47,9 @@ class TokenEmbedding(Part):
         if self.positions:
             if positions is None:
                 raise ValueError("an embedding with a position table needs the tokens' positions")
-            ops.embed(ids, self.table, out, self.pos_table, positions)
+            ops.embed(ids, self.table, out, self.pos_table, positions, scale=self.scale)
         else:
-            ops.embed(ids, self.table, out)
+            ops.embed(ids, self.table, out, scale=self.scale)
         return out
 
 

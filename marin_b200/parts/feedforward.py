@@ -11,7 +11,7 @@ from typing import Dict, List
 import torch
 
 from ..kernels import ops
-from .base import Part, Runtime
+from .base import Part, Runtime, element_size
 from .registry import register_feedforward
 from .spec import TensorSpec
 
@@ -106,4 +106,71 @@ class PolyNormMLP(FeedForward):
         ops.polynorm(z, self.coef, self.eps, act)
         ops.stage_name = "down"
         ops.gemm(act, self.w_down, residual, accumulate=True)
+        return None
+
+
+@register_feedforward("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of small SwiGLU feed-forwards of which every token uses ``top``: ``out = sum_e expert_e(.)`` over the chosen ones.
+
+    Router: ``z = h W_r^T`` in float32 (the matrix is kept in float32), scores ``sigmoid(z)`` (``score="sigmoid"``) or the
+    softmax of ``z`` over all experts; the ``top`` largest are chosen (the lower expert among equals) and their scores are
+    the weights, divided by their sum if ``renormalize``.  ``weight_on`` "input": the weight multiplies what the expert
+    reads, ``expert(w h)``, so it passes through the activation; "output": ``w expert(h)``.  Experts have no biases:
+    ``down( silu(gate x) * (up x) )``.  Nothing is read back to the host: routing, grouping and the experts' products
+    are kernels over device arrays, so single-token steps can be captured in graphs.
+    ``names``: the router's tensor and the pattern of an expert's tensors inside ``name`` (``{e}`` the expert's number)."""
+
+    NAMES = {"router": "router.weight", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+             "down": "experts.{e}.down_proj.weight"}
+
+    def __init__(self, hidden: int, intermediate: int, experts: int, top: int, name: str, score: str = "sigmoid",
+                 renormalize: bool = False, weight_on: str = "input", names=None):
+        self.hidden, self.intermediate, self.experts, self.top, self.name = int(hidden), int(intermediate), int(experts), int(top), name
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"routed_experts: top {top} of {experts} experts")
+        if score not in ops.SCORE_MODES or weight_on not in ("input", "output"):
+            raise ValueError(f"routed_experts: score {score!r} / weight_on {weight_on!r}")
+        self.score, self.renormalize, self.weight_on = score, bool(renormalize), weight_on
+        self.names = dict(self.NAMES, **(names or {}))
+        self.router = self.w_gate_up = self.w_down = None
+
+    def _n(self, key: str, e: int = 0) -> str:
+        return f"{self.name}.{self.names[key].format(e=e)}"
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, i = self.hidden, self.intermediate
+        specs = []
+        for e in range(self.experts):
+            specs += [TensorSpec(self._n("gate", e), (i, h)), TensorSpec(self._n("up", e), (i, h)), TensorSpec(self._n("down", e), (h, i))]
+        return specs + [TensorSpec(self._n("router"), (self.experts, h), "bias")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        # one tensor per kind for all experts: gate rows then up rows of an expert side by side, [E, 2 ff, h]; down [E, h, ff]
+        self.w_gate_up = rt.matrix(torch.stack([torch.cat([tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e))], dim=0)
+                                                for e in range(self.experts)]))
+        self.w_down = rt.matrix(torch.stack([tensors.pop(self._n("down", e)) for e in range(self.experts)]))
+        self.router = rt.f32(tensors.pop(self._n("router")))
+        self.rt = rt
+
+    def bytes_read(self, tokens: int, dtype) -> int:
+        """Only the experts that some token chose are read: at most ``tokens * top`` of them."""
+        per_expert = 3 * self.hidden * self.intermediate * element_size(dtype)
+        return min(self.experts, tokens * self.top) * per_expert + self.experts * self.hidden * 4
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return 2.0 * tokens * self.hidden * (self.experts + 3 * self.top * self.intermediate)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.moe_jobs(dtype, self.hidden, self.intermediate)
+
+    def forward(self, x, ctx, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        chosen = ws.get("moe_experts", (T, self.top), torch.int32)
+        weights = ws.get("moe_weights", (T, self.top), torch.float32)
+        ops.stage_name = "router"
+        ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize)
+        ops.stage_name = "experts"
+        ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws)
         return None

@@ -307,3 +307,137 @@ class SigmoidAttention(Mixer):
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None
+
+
+@register_mixer("sink_attention")
+class SinkAttention(Mixer):
+    """Causal grouped-query softmax attention over the paged cache, with the variations a design may switch on one by one.
+
+    ``q, k, v = x W^T (+ b)`` (``bias``); value heads ``v_head_dim`` wide.  RMS norm of q and k before the rotation:
+    ``qk_norm`` "head" (per head over ``head_dim``, one weight ``[head_dim]`` each), "whole" (over the whole projection at
+    once, before it is split into heads, weights ``[heads head_dim]`` and ``[kv_heads head_dim]``) or None.  The rotation
+    comes from ``position`` (any registered encoding: partial width, rescaled frequencies and magnitudes are its
+    business).  Score ``q . k * scale``.  A position sees the keys before it and itself; ``window`` keeps the last so
+    many, ``chunk`` keeps those of its own chunk (``floor(i / chunk) = floor(j / chunk)``, counted from the sequence's
+    first position wherever a prompt was cut).  ``sink``: the softmax has one more term in its denominator, a key of
+    score 0 without a value: ``p_j = exp(s_j) / (1 + sum_j exp(s_j))``.
+
+    ``value_mix``: None, or a name that ties layers together: the first layer of that name in the model leaves its values
+    (of the step's tokens) where the later ones find them, and those cache ``(1 - lam) v + lam v_first`` with their own
+    learned ``lam`` (``first_of_mix`` says which a layer is; the first one's ``lam`` tensor is expected and unused).
+    ``gate``: the heads' outputs are multiplied by ``sigmoid(x W_g^T)`` before the output projection.  One fused product
+    makes q | k | v | g.
+    """
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "g": "g_proj.weight",
+             "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "lam": "value_mix"}
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, name: str, position: PartSpec,
+                 v_head_dim: Optional[int] = None, scale: Optional[float] = None, bias: bool = False, qk_norm: Optional[str] = "head",
+                 norm_eps: float = 1e-6, window: Optional[int] = None, chunk: Optional[int] = None, sink: bool = True,
+                 value_mix: Optional[str] = None, first_of_mix: bool = False, gate: bool = False, names=None):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.heads % self.kv_heads != 0:
+            raise ValueError(f"{heads} heads cannot share {kv_heads} kv heads evenly")
+        if qk_norm not in (None, "head", "whole"):
+            raise ValueError(f"qk_norm {qk_norm!r} is not one of None, 'head', 'whole'")
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else self.head_dim
+        self.name, self.bias, self.qk_norm, self.norm_eps = name, bool(bias), qk_norm, float(norm_eps)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.window = int(window) if window else None
+        self.chunk = int(chunk) if chunk else None
+        self.sink, self.gate = bool(sink), bool(gate)
+        self.value_mix, self.first_of_mix = value_mix, bool(first_of_mix)
+        self.position = lookup("position", position.kind)(**position.params)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.q_dim, self.k_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        self.v_dim, self.o_dim = self.kv_heads * self.v_head_dim, self.heads * self.v_head_dim
+        self.w_in = self.w_o = self.q_weight = self.k_weight = self.q_b = self.k_b = self.v_b = self.lam = None
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        # (a chunked mask never looks behind its chunk's start, but pages are not given back there: the keys a window
+        # has passed are dropped by the cache manager, a chunk's are only skipped)
+        return PagedKV(self.kv_heads, self.head_dim, self.window, self.v_head_dim)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h = self.hidden
+        specs = [TensorSpec(self._n("q"), (self.q_dim, h)), TensorSpec(self._n("k"), (self.k_dim, h)),
+                 TensorSpec(self._n("v"), (self.v_dim, h)), TensorSpec(self._n("o"), (h, self.o_dim))]
+        if self.gate:
+            specs.append(TensorSpec(self._n("g"), (self.o_dim, h)))
+        if self.bias:
+            specs += [TensorSpec(self._n("q_bias"), (self.q_dim,), "bias"), TensorSpec(self._n("k_bias"), (self.k_dim,), "bias"),
+                      TensorSpec(self._n("v_bias"), (self.v_dim,), "bias")]
+        if self.qk_norm is not None:
+            n = 1 if self.qk_norm == "head" else None
+            specs += [TensorSpec(self._n("q_norm"), (self.head_dim if n else self.q_dim,), "norm"),
+                      TensorSpec(self._n("k_norm"), (self.head_dim if n else self.k_dim,), "norm")]
+        if self.value_mix is not None:
+            specs.append(TensorSpec(self._n("lam"), (), "bias", 0.5))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        parts = [tensors.pop(self._n(p)) for p in "qkv"]
+        if self.gate:
+            parts.append(tensors.pop(self._n("g")))
+        self.w_in = rt.matrix(torch.cat(parts, dim=0))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        if self.bias:
+            self.q_b, self.k_b, self.v_b = (rt.f32(tensors.pop(self._n(f"{p}_bias"))) for p in "qkv")
+        if self.qk_norm is not None:
+            self.q_weight = rt.f32(tensors.pop(self._n("q_norm")))
+            self.k_weight = rt.f32(tensors.pop(self._n("k_norm")))
+        if self.value_mix is not None:
+            self.lam = rt.f32(tensors.pop(self._n("lam"))).reshape(1)
+        self.position.load(tensors, rt)
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + self.v_head_dim)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.sink_attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim, self.v_head_dim)
+
+    def decode_plan_key(self):
+        return ("sink_attention", self.heads, self.kv_heads, self.head_dim, self.v_head_dim, self.chunk, self.window)
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        return ops.sink_decode_plan(rt.dtype, requests, self.heads, self.kv_heads, self.head_dim, self.v_head_dim, span,
+                                    self.window or 0, self.chunk or 0)
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        writes = cache.owner
+        if not writes and self.gate:
+            raise ValueError("sink_attention: a gated layer cannot read another run's cache")   # its columns lie behind k and v
+        w = self.w_in if writes else self.w_in[: self.q_dim]
+        ops.stage_name = "q|k|v|g"
+        rows = ws.get("qkvg", (T, w.shape[0]), x.dtype)
+        ops.gemm(x, w, rows)
+        ops.stage_name = "heads"
+        q = ws.get("q", (T, self.q_dim), x.dtype)
+        shared = None
+        mode = None
+        if self.value_mix is not None and writes:
+            # the first layer's values of this step's tokens, for the later layers of the same name
+            shared = ws.get(f"values:{self.value_mix}", (T, self.v_dim), x.dtype)
+            mode = "leave" if self.first_of_mix else "mix"
+        pos = self.position
+        ops.qkv_finish(rows, q, self.q_b, self.k_b, self.v_b, self.qk_norm, self.q_weight, self.k_weight, self.norm_eps, ctx.positions,
+                       pos.inv_freq, pos.rotary_dim, pos.magnitude, cache.slot_mapping, cache.k, cache.v, mode, shared, self.lam,
+                       self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes)
+        out = ws.get("attn_out", (T, self.o_dim), x.dtype)
+        ops.stage_name = "attention"
+        gate = rows[:, self.q_dim + self.k_dim + self.v_dim:] if self.gate else None
+        plans = ctx.decode_plans
+        ops.attention_sink(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads, self.head_dim, self.v_head_dim,
+                           self.scale, self.window or 0, self.chunk or 0, self.sink, gate,
+                           plans.get(self.decode_plan_key()) if plans else None)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None

@@ -17,18 +17,20 @@ class RMSNorm(Part):
 
     The weight multiplies directly (no ``1 + w``), as the reference computes it
     (crates/tensor/src/norm.rs:16-22, crates/cuda/src/kernels.cu:51-58); ``unit_offset``
-    selects the ``1 + w`` form other architectures use.
+    selects the ``1 + w`` form other architectures use (their weights lie around zero).  ``tensor`` names the weight
+    inside ``name`` where it is not ``weight`` ("" for the tensor ``name`` itself).
     """
 
-    def __init__(self, dim: int, eps: float, name: str, unit_offset: bool = False):
+    def __init__(self, dim: int, eps: float, name: str, unit_offset: bool = False, tensor: str = "weight"):
         self.dim, self.eps, self.name, self.unit_offset = int(dim), float(eps), name, bool(unit_offset)
+        self.weight_name = f"{name}.{tensor}" if tensor else name
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(f"{self.name}.weight", (self.dim,), "norm")]
+        return [TensorSpec(self.weight_name, (self.dim,), "norm", 0.0 if self.unit_offset else None)]
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
-        self.weight = rt.f32(tensors.pop(f"{self.name}.weight"))
+        self.weight = rt.f32(tensors.pop(self.weight_name))
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``x`` float32 ``[rows, dim]`` → ``out`` (float32 or bfloat16) ``[rows, dim]``."""

@@ -6,6 +6,7 @@ parameters.  ``NoPosition`` hands over nothing and the mixer skips the rotation.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -20,6 +21,8 @@ class PositionEncoding(Part):
     rotary_dim: int = 0
     #: False: element i pairs with i + rotary_dim/2 ("rotate half"); True: (2i, 2i+1)
     interleaved: bool = False
+    #: what sines and cosines are multiplied by (1 unless a rescaled encoding says otherwise)
+    magnitude: float = 1.0
 
 
 @register_position("rope")
@@ -44,6 +47,44 @@ class Rotary(PositionEncoding):
         i = torch.arange(half, dtype=torch.float32)
         exponent = -(i * 2.0 / float(self.rotary_dim))
         self.inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent).to(rt.device)
+
+
+@register_position("rope_yarn")
+class RescaledRotary(Rotary):
+    """Rotary embedding whose frequencies are stretched for contexts longer than the ``original`` one (YaRN: Peng, Quesnelle,
+    Fan, Shippole, "YaRN: Efficient Context Window Extension of Large Language Models").  With ``f_i = theta^(-2i/d)``
+    and ``dim(t) = d ln(original / (2 pi t)) / (2 ln theta)`` (the pair that makes ``t`` turns over the original context):
+    ``lo = max(floor(dim(fast)), 0)``, ``hi = min(ceil(dim(slow)), d - 1)``, ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``;
+    pair ``i`` turns at ``f_i / factor * ramp_i + f_i (1 - ramp_i)``: fast pairs keep their frequency, slow ones are divided by
+    ``factor``, those between are blended.  Sines and cosines are multiplied by ``0.1 ln(factor) + 1``.  The table is made in
+    float64 on the host and rounded once to float32; angles are float32 products of it."""
+
+    def __init__(self, head_dim: int, theta: float, factor: float, original: float, fast: float, slow: float,
+                 rotary_dim: Optional[int] = None, interleaved: bool = False):
+        super().__init__(head_dim, theta, rotary_dim, interleaved)
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+        if self.factor <= 0 or self.original <= 0 or self.fast <= 0 or self.slow <= 0 or self.theta <= 1:
+            raise ValueError("rope_yarn: factor, original, fast and slow must be positive and theta above 1")
+        self.magnitude = 0.1 * math.log(self.factor) + 1.0
+
+    def frequencies(self):
+        """The angle per position of every pair, as Python floats (float64)."""
+        d, half = self.rotary_dim, self.rotary_dim // 2
+
+        def dim_of(turns: float) -> float:
+            return d * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(dim_of(self.fast)), 0)
+        hi = min(math.ceil(dim_of(self.slow)), d - 1)
+        out = []
+        for i in range(half):
+            f = self.theta ** (-2.0 * i / d)
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / self.factor * ramp + f * (1.0 - ramp))
+        return out
+
+    def load(self, tensors, rt: Runtime) -> None:
+        self.inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32).to(rt.device)
 
 
 @register_position("none")

@@ -18,12 +18,14 @@ class TensorSpec:
     ``role`` decides storage and random initialisation: ``matrix`` (bf16 or f32,
     N(0, 0.02)), ``norm`` (kept f32 on the device, 1 + N(0, 0.05)), ``bias`` (kept f32 on
     the device, N(0, 0.02): offsets, mixing coefficients, small tables added to scores),
-    ``table`` (an embedding table, treated like a matrix), ``int_table`` (int32).
+    ``table`` (an embedding table, treated like a matrix), ``int_table`` (int32).  ``mean`` moves the centre of the random
+    initialisation (a mixing coefficient that should start near 1 or near 1/n rather than near 0).
     """
 
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
+    mean: Optional[float] = None
 
 
 @dataclass
@@ -46,6 +48,8 @@ class LayerSpec:
     prefix: str
     #: names inside ``prefix`` of the sub-modules, so that parts find their tensors
     names: Dict[str, str] = field(default_factory=dict)
+    #: what the block arrangement itself is built from, besides its parts (a hyper-connection block: the number of streams)
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass
@@ -68,3 +72,6 @@ class ModelSpec:
     schedule: List[ScheduleEntry]
     #: tensors that may be present in a checkpoint and are ignored (e.g. an unused head when tied)
     ignorable: Tuple[str, ...] = ()
+    #: how many copies of the residual stream the blocks keep (hyper-connections); the model hands its blocks a float32
+    #: ``[streams, T, hidden]`` tensor when there are more than one, and the head reads their sum
+    streams: int = 1

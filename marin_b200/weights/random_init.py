@@ -49,7 +49,9 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu",
             out[at:at + rows] = ((1.0 + norm_std * part) if spec.role == "norm" else matrix_std * part).to(dtype)
         return out
     values = torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32)
-    if spec.role == "norm":
+    if spec.mean is not None:
+        values = spec.mean + matrix_std * values
+    elif spec.role == "norm":
         values = 1.0 + norm_std * values
     else:
         values = matrix_std * values
