@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, with their fractions of roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-    python bench.py --arch lakulix [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
+    python bench.py --arch lakulix|fegarax [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
 
 The default run has the layer sizes of the Qwen3-4B layout with random bfloat16 weights, a batch of 8
 sequences and a context of 4096 positions (the last timed step reaches it).  A "step" is one decode
@@ -19,7 +19,9 @@ step.  One JSON line is printed:
 ``--arch lakulix`` measures another architecture instead, beside the Qwen3 layout of the same width, depth and vocabulary:
 Lakulix layers (linear attention, sigmoid attention, time mixing, in turn; a PolyNorm feed-forward in each) at the chosen
 layout's sizes, decode at the given batch and the prompt step, each with its fraction of roofline, as one JSON line of
-its own form (``--profile``: its stage tables).  The default workload and its line are not touched by it.
+its own form (``--profile``: its stage tables).  ``--arch fegarax`` does the same for Fegarax layers (four residual streams,
+attention with the layout's heads, a gate and a sink, eight experts of half the feed-forward width of which two are chosen).
+The default workload and its line are not touched by either.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else 6.65 TB/s and 1.59 PFLOP/s.
 Between timed iterations nothing is flushed: a decode step reads gigabytes of weights, far more than the
@@ -314,29 +316,49 @@ def lakulix_layout(raw: dict, layers: int) -> dict:
             "layers": [dict(mixers[i % 3], mlp={"kind": "dense", "ff": raw["intermediate_size"]}) for i in range(layers)]}
 
 
-def lakulix_mode(args, pk) -> int:
-    """Decode and prompt throughput of Lakulix at a Qwen3 layout's sizes, and of that Qwen3 layout at the same depth, with
-    their fractions of roofline: one JSON line.  With --profile: Lakulix's stage tables."""
+FEGARAX_LAYERS = ("four residual streams; attention with the layout's heads (values as wide as keys, rotation of half of every head with "
+                  "rescaled frequencies, chunks of 8,192 positions: every earlier key is seen at this context, as in the Qwen3 arm), "
+                  "a gate, a sink, values mixed with the first layer's; 8 experts of half the layout's feed-forward width, 2 chosen "
+                  "(as many active feed-forward weights as the dense layout, four times as many in memory)")
+
+
+def fegarax_layout(raw: dict, layers: int) -> dict:
+    """A Fegarax configuration at a Qwen3 layout's sizes: the same width, vocabulary and attention heads; experts that
+    together activate as many feed-forward weights per token as the layout's dense feed-forward."""
+    head = raw["head_dim"]
+    mixer = {"heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "dim": head, "vdim": head, "scale": head ** -0.5,
+             "mask": {"size": 2 * CONTEXT}, "v_mix": True,
+             "rot": {"base": 1000000.0, "dims": head // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "expert": {"ff": raw["intermediate_size"] // 2}, "router": {"experts": 8, "top": 2}}
+    return {"architecture": "Fegarax", "vocab": raw["vocab_size"], "width": raw["hidden_size"], "streams": 4, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "max_positions": 2 * CONTEXT, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
+
+
+def arch_mode(args, pk, arch: str) -> int:
+    """Decode and prompt throughput of another architecture at a Qwen3 layout's sizes, and of that Qwen3 layout at the same
+    depth, with their fractions of roofline: one JSON line.  With --profile: the architecture's stage tables."""
     import gc
 
     import torch
 
     from marin_b200 import Engine
-    from marin_b200.config import LakulixConfig, Qwen3Config
+    from marin_b200.config import FegaraxConfig, LakulixConfig, Qwen3Config
 
     layers = args.layers or 12
     raw = dict(LAYOUTS[args.model], num_hidden_layers=layers)
     warmup = max(3, args.warmup)
-    arms = {"lakulix": LakulixConfig.from_dict(lakulix_layout(raw, layers)), "qwen3": Qwen3Config.from_dict(raw)}
+    title = arch.capitalize()
+    other = LakulixConfig.from_dict(lakulix_layout(raw, layers)) if arch == "lakulix" else FegaraxConfig.from_dict(fegarax_layout(raw, layers))
+    arms = {arch: other, "qwen3": Qwen3Config.from_dict(raw)}
     out = {}
     for name, cfg in arms.items():
-        if args.profile and name != "lakulix":
+        if args.profile and name != arch:
             continue
         engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, max_batch=max(args.batch, 8),
                         token_budget=PREFILL_TOKENS)
         fill_cache(engine)
         if args.profile:
-            return profile_mode(engine, args, pk, f"Lakulix at the Qwen3-{args.model.upper()} layout's sizes, {layers} layers", batches=(1, args.batch))
+            return profile_mode(engine, args, pk, f"{title} at the Qwen3-{args.model.upper()} layout's sizes, {layers} layers", batches=(1, args.batch))
         weight_bytes, prefill_flops = model_bytes_and_flops(engine, args.batch, PREFILL_TOKENS)
         kv_tok = kv_bytes_per_token(engine)
         clocks = ClockSampler(ClockSampler.gpu_in_use())
@@ -360,15 +382,16 @@ def lakulix_mode(args, pk) -> int:
         gc.collect()
         torch.cuda.empty_cache()
     print(json.dumps({
-        "metric": f"Lakulix beside the Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
+        "metric": f"{title} beside the Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
                   f"(context {CONTEXT}), prefill tok/s at {PREFILL_TOKENS} tokens, fractions of roofline",
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "dtype": "bf16", "higher_is_better": True,
         "data": "synthetic (uniform random token ids, seeded random weights)", "peaks": pk,
         "config": {"layers": layers, "width": raw["hidden_size"], "ff": raw["intermediate_size"], "vocab": raw["vocab_size"],
                    "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": PAGE,
-                   "lakulix_layers": "lightning (heads of 128 x 128), attention (the layout's heads), wkv (heads of 64) in turn, a dense feed-forward in each",
+                   f"{arch}_layers": FEGARAX_LAYERS if arch == "fegarax" else
+                   "lightning (heads of 128 x 128), attention (the layout's heads), wkv (heads of 64) in turn, a dense feed-forward in each",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB)"},
-        "lakulix": out["lakulix"], "qwen3": out["qwen3"], "impl": "ours"}))
+        arch: out[arch], "qwen3": out["qwen3"], "impl": "ours"}))
     return 0
 
 
@@ -393,20 +416,20 @@ def main() -> int:
     ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the last timed decode step reaches (default 4096)")
     ap.add_argument("--profile", action="store_true", help="print where a step's time goes, stage by stage, instead of the JSON line")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix"],
-                    help="qwen3: the default workload; lakulix: that architecture at the layout's sizes beside the Qwen3 layout of equal size")
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix", "fegarax"],
+                    help="qwen3: the default workload; lakulix, fegarax: that architecture at the layout's sizes beside the Qwen3 layout of equal size")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     CONTEXT = args.context
-    if args.arch == "lakulix":
+    if args.arch != "qwen3":
         if args.gpus != 1:
             print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
             return 2
         from marin_b200.kernels import build as _build
 
         _build.build_all(verbose=False)
-        return lakulix_mode(args, peaks())
+        return arch_mode(args, peaks(), args.arch)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

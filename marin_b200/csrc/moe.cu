@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const T* __res
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
+        if (at >= E) at = c;                                   // logits that are not numbers order nothing: stay inside the table
         const float score = score_mode == 1 ? expf(best - zmax) / denom : 1.0f / (1.0f + expf(-best));
         chosen_sum += score;
         if (lane == 0) {
@@ -197,4 +198,194 @@ MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gat
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
     return MB_ERR_BAD_DTYPE;
+}
+
+// ---- bf16 experts on the tensor cores (mma.sync): pairs sorted by expert, one grouped product per projection --------------
+// 1. gather: xs[i] = bf16(w h[token]) of the i-th pair in expert order (w = 1 where the weight goes on the output), with the
+//    pair's token and weight beside it and, for every pair, where it went (inv).
+// 2. gate|up: act[i][c] = silu(gate_c . xs[i]) * (up_c . xs[i]); a CTA takes 64 pairs of one expert x 64 columns, both
+//    projections of those columns side by side (two accumulators), K in steps of 64 through a 3-stage cp.async ring.
+// 3. down: out[i][:] = down . act[i]; with one choice per token it adds straight into y[token] (no two pairs share a row),
+//    otherwise it leaves float32 rows that a last kernel adds into y in choice order.
+// A pair's row is computed from that row's operands alone, whichever tile it lands in.
+#include "mma_helpers.cuh"
+
+#define GM 64
+#define GN 64
+#define GK 64
+#define GLD (GK + 8)
+#define G_STAGES 3
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h_rows, const int* __restrict__ order, const float* __restrict__ weight_of,
+                                  T* __restrict__ xs, int* __restrict__ token_sorted, float* __restrict__ weight_sorted,
+                                  int* __restrict__ inv, int h, int top, int weight_on_input) {
+    PDL_ENTER();
+    h_rows = pdl_fresh(h_rows); order = pdl_fresh(order); weight_of = pdl_fresh(weight_of);
+    const int i = blockIdx.x;
+    const int p = order[i];
+    const int token = p / top;
+    const float w = weight_of[p];
+    if (threadIdx.x == 0) { token_sorted[i] = token; weight_sorted[i] = w; inv[p] = i; }
+    const float f = weight_on_input ? w : 1.0f;
+    for (int c = threadIdx.x; c < h; c += blockDim.x) xs[(size_t)i * h + c] = from_f32<T>(to_f32(h_rows[(size_t)token * h + c]) * f);
+}
+
+// MODE 0: W [E][2 N][K] (gate rows, then up rows), result silu(gate) * up as bf16 [rows][N].
+// MODE 1: W [E][N][K], result float32: row r goes to dst_rows[r] (null: r), times row_scale[r] (null: 1), added if `accumulate`.
+template <int MODE>
+__global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
+                                                          const int* __restrict__ offsets, int E, int N, int K, bf16* __restrict__ act_out,
+                                                          float* __restrict__ f_out, const int* __restrict__ dst_rows,
+                                                          const float* __restrict__ row_scale, int accumulate) {
+    PDL_ENTER();
+    A = pdl_fresh(A); offsets = pdl_fresh(offsets); dst_rows = pdl_fresh(dst_rows); row_scale = pdl_fresh(row_scale); f_out = pdl_fresh(f_out);
+    constexpr int NB = MODE == 0 ? 2 : 1;
+    extern __shared__ __align__(16) uint8_t g_smem[];
+    bf16* sA = reinterpret_cast<bf16*>(g_smem);                              // [G_STAGES][GM][GLD]
+    bf16* sB = sA + G_STAGES * GM * GLD;                                     // [G_STAGES][NB][GN][GLD]
+    // which expert's which tile this CTA is: tiles are numbered expert after expert
+    int tile = blockIdx.x, e = 0, row0 = -1, row_end = 0;
+    for (e = 0; e < E; ++e) {
+        const int b = offsets[e], n = offsets[e + 1] - b;
+        const int tiles = (n + GM - 1) / GM;
+        if (tile < tiles) { row0 = b + tile * GM; row_end = b + n; break; }
+        tile -= tiles;
+    }
+    if (row0 < 0) return;
+    const int col0 = blockIdx.y * GN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bf16* We = W + (size_t)e * NB * N * K;
+    auto load = [&](int stage, int kt) {
+        const int k0 = kt * GK;
+        bf16* a = sA + stage * GM * GLD;
+        for (int idx = threadIdx.x; idx < GM * (GK / 8); idx += 128) {
+            const int r = idx / (GK / 8), c = idx % (GK / 8);
+            bf16* dst = a + r * GLD + c * 8;
+            if (row0 + r < row_end) cp_async16(dst, A + (size_t)(row0 + r) * K + k0 + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            bf16* b = sB + (stage * NB + nb) * GN * GLD;
+            for (int idx = threadIdx.x; idx < GN * (GK / 8); idx += 128) {
+                const int r = idx / (GK / 8), c = idx % (GK / 8);
+                bf16* dst = b + r * GLD + c * 8;
+                if (col0 + r < N) cp_async16(dst, We + ((size_t)nb * N + col0 + r) * K + k0 + c * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    float acc[NB][GN / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int j = 0; j < GN / 8; ++j) { acc[nb][j][0] = acc[nb][j][1] = acc[nb][j][2] = acc[nb][j][3] = 0.0f; }
+    const int nk = K / GK;
+#pragma unroll
+    for (int s = 0; s < G_STAGES - 1; ++s) {
+        if (s < nk) load(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < nk; ++kt) {
+        cp_async_wait<G_STAGES - 2>();
+        __syncthreads();                                       // stage kt is there, and everyone is done with stage kt - 1
+        if (kt + G_STAGES - 1 < nk) load((kt + G_STAGES - 1) % G_STAGES, kt + G_STAGES - 1);
+        cp_async_commit();
+        const int stage = kt % G_STAGES;
+        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sA + stage * GM * GLD + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * GLD + (lane >> 4) * 8);
+#pragma unroll
+        for (int kk = 0; kk < GK / 16; ++kk) {
+            uint32_t a[4];
+            ldsm_x4(a_addr + kk * 32, a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(sB + (stage * NB + nb) * GN * GLD + ((lane & 7) + (lane >> 4) * 8) * GLD + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                for (int j = 0; j < GN / 8; j += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(b_addr + (uint32_t)(j * 8 * GLD * 2 + kk * 32), b0, b1, b2, b3);
+                    mma_bf16_16816(acc[nb][j], a, b0, b1);
+                    mma_bf16_16816(acc[nb][j + 1], a, b2, b3);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int col = col0 + 2 * (lane & 3);
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = row0 + warp * 16 + (lane >> 2) + 8 * rr;
+        if (row >= row_end) continue;
+        if (MODE == 0) {
+            bf16* dst = act_out + (size_t)row * N;
+#pragma unroll
+            for (int j = 0; j < GN / 8; ++j) {
+                const int c = col + j * 8;
+                if (c < N) {                                   // N is even: a pair of columns is inside or outside together
+                    const float g0 = acc[0][j][2 * rr], g1 = acc[0][j][2 * rr + 1];
+                    const float u0 = acc[NB - 1][j][2 * rr], u1 = acc[NB - 1][j][2 * rr + 1];
+                    *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                }
+            }
+        } else {
+            const size_t to = dst_rows != nullptr ? (size_t)dst_rows[row] : (size_t)row;
+            const float f = row_scale != nullptr ? row_scale[row] : 1.0f;
+            float* dst = f_out + to * N;
+#pragma unroll
+            for (int j = 0; j < GN / 8; ++j) {
+                const int c = col + j * 8;
+                if (c < N) {
+                    float2 v = make_float2(acc[0][j][2 * rr] * f, acc[0][j][2 * rr + 1] * f);
+                    if (accumulate) { const float2 old = *reinterpret_cast<const float2*>(dst + c); v.x += old.x; v.y += old.y; }
+                    *reinterpret_cast<float2*>(dst + c) = v;
+                }
+            }
+        }
+    }
+}
+
+// y[t][c] += sum over the token's choices, in choice order, of rows[inv[t top + choice]][c]
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ inv, float* __restrict__ y, int h, int top) {
+    PDL_ENTER();
+    rows = pdl_fresh(rows); inv = pdl_fresh(inv); y = pdl_fresh(y);
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < h; c += blockDim.x) {
+        float a = y[(size_t)t * h + c];
+        for (int k = 0; k < top; ++k) a += rows[(size_t)inv[t * top + k] * h + c];
+        y[(size_t)t * h + c] = a;
+    }
+}
+
+#define G_SMEM(NB) (G_STAGES * (GM + (NB) * GN) * GLD * 2)
+
+// Whether the tensor-core path takes these sizes: both inner sizes in whole steps of 64, rows 16-byte aligned.
+MB_API int mb_moe_fast_supported(int h, int ff) { return h % GK == 0 && ff % GK == 0 && h % 8 == 0 && ff % 8 == 0; }
+
+// xs bf16 [pairs][h], act bf16 [pairs][ff], rows float32 [pairs][h] (unused with top = 1), the int and float arrays [pairs].
+MB_API int mb_moe_experts_fast(const void* h_rows, const void* w_gate_up, const void* w_down, const int* expert_of, const float* weight_of,
+                               int* offsets, int* order, int* inv, int* token_sorted, float* weight_sorted, void* xs, void* act,
+                               float* rows, float* y, int tokens, int h, int ff, int E, int top, int weight_on_input, cudaStream_t s) {
+    if (tokens <= 0) return 0;
+    if (!mb_moe_fast_supported(h, ff) || E <= 0 || top <= 0 || (size_t)E * 8 > 48 * 1024) return MB_ERR_BAD_SIZE;
+    const int pairs = tokens * top;
+    int rc = launch_kernel(moe_group_kernel, 1, 1024, (size_t)E * 8, s, 0, expert_of, pairs, E, offsets, order);
+    if (rc != 0) return rc;
+    rc = launch_kernel(moe_gather_kernel<bf16>, pairs, 128, 0, s, 0, (const bf16*)h_rows, (const int*)order, weight_of, (bf16*)xs, token_sorted,
+                       weight_sorted, inv, h, top, weight_on_input);
+    if (rc != 0) return rc;
+    const int tiles = pairs / GM + E < pairs ? pairs / GM + E : pairs;          // at most one partial tile per expert
+    cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(2));
+    cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(1));
+    rc = launch_kernel(moe_grouped_kernel<0>, dim3(tiles, (ff + GN - 1) / GN), 128, G_SMEM(2), s, 0, (const bf16*)xs, (const bf16*)w_gate_up,
+                       (const int*)offsets, E, ff, h, (bf16*)act, (float*)nullptr, (const int*)nullptr, (const float*)nullptr, 0);
+    if (rc != 0) return rc;
+    const float* scale = weight_on_input ? nullptr : weight_sorted;
+    if (top == 1)
+        return launch_kernel(moe_grouped_kernel<1>, dim3(tiles, (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act, (const bf16*)w_down,
+                             (const int*)offsets, E, h, ff, (bf16*)nullptr, y, (const int*)token_sorted, scale, 1);
+    rc = launch_kernel(moe_grouped_kernel<1>, dim3(tiles, (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act, (const bf16*)w_down,
+                       (const int*)offsets, E, h, ff, (bf16*)nullptr, rows, (const int*)nullptr, scale, 0);
+    if (rc != 0) return rc;
+    return launch_kernel(moe_combine_kernel, tokens, 256, 0, s, 0, (const float*)rows, (const int*)inv, y, h, top);
 }

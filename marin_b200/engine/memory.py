@@ -67,7 +67,7 @@ def workspace_bytes(model, dtype: torch.dtype, token_budget: int, max_batch: int
         width = sum(int(s.shape[0]) for s in part.tensor_specs() if s.role == "matrix" and len(s.shape) == 2)
         widest = max(widest, width)
     hidden, vocab = model.spec.hidden_size, model.spec.vocab_size
-    per_token = 4 * hidden * (1 + int(getattr(model.spec, "streams", 1))) + size * (2 * hidden + 2 * widest)
+    per_token = 4 * hidden * (1 + max(1, int(getattr(model.spec, "streams", 0)))) + size * (2 * hidden + 2 * widest)
     logits = 4 * vocab * max_batch
     graphs = sum(b * (4 * vocab + per_token) for b in graph_sizes)
     scratch = 96 << 20

@@ -1217,9 +1217,37 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         gate_stride = gate.stride(0)
     if T == 0:
         return
+    size = q.element_size()
+    per_row = H * (d + (3 if gate is not None else 2) * dv) * size
+    if use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0:
+        lib = _sink_lib(d, dv, H // K)
+        max_pages = block_table.shape[1]
+        nd = ctx.num_decode
+        if nd > 0:
+            if plan is None:
+                plan = sink_decode_plan(q.dtype, nd, H, K, d, dv, ctx.max_seq_len, window, chunk)
+            acc = ctx.workspace.get("sink_parts", (plan.chunks, nd, H, dv), torch.float32)
+            ml = ctx.workspace.get("sink_part_sums", (plan.chunks, nd, H, 2), torch.float32)
+            if launch_log is not None:
+                _cost(nd * per_row + 2 * _size(acc), 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+                _pending_cost["rows"] = "decode"
+            _check(lib.mb_attn_sink_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(acc), _ptr(ml), _ptr(block_table),
+                                           _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
+                                           _c_int(window), _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride),
+                                           _c_int(plan.split), _c_int(plan.chunks), _stream()), "attention (sink, decode)")
+            launches_extra(1)
+        if ctx.num_requests > nd:
+            if launch_log is not None:
+                _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+                _pending_cost["rows"] = "prefill"
+            _check(lib.mb_attn_sink_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                            _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                                            _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_int(window),
+                                            _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _stream()),
+                   "attention (sink, prefill)")
+        return
     if launch_log is not None:
-        size = q.element_size()
-        _cost(T * H * (d + (3 if gate is not None else 2) * dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+        _cost(T * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
         _pending_cost["rows"] = "all"
     _check(_lib("mb_attention_sink").mb_attention_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
@@ -1227,13 +1255,56 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _stream()), "attention (sink)")
 
 
+#: bf16 sink attention goes to the tensor-core kernels where the head layout allows (False: always the plain kernel)
+use_fast_sink_attention = True
+
+
+def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int) -> bool:
+    return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 128 and 16 <= dv <= 128
+            and H % K == 0 and 1 <= H // K <= 8)
+
+
+def _sink_job(d: int, dv: int, group: int) -> tuple:
+    return (["attention_sink_fast.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}"])
+
+
+def _sink_lib(d: int, dv: int, group: int):
+    return build.load(f"mb_attention_sink_fast_d{d}_v{dv}_g{group}", *_sink_job(d, dv, group))
+
+
 def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
-    return library_jobs("mb_attention_sink")
+    """The kernels a sink-attention mixer of this head layout runs: the head preparation and the plain kernel, and the
+    tensor-core kernels compiled for the layout where it allows."""
+    jobs = library_jobs("mb_attention_sink")
+    if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv):
+        jobs[f"mb_attention_sink_fast_d{d}_v{dv}_g{H // K}"] = _sink_job(d, dv, H // K)
+    return jobs
+
+
+class SinkDecodePlan:
+    """How single-token sink attention splits the keys a token sees over CTAs: ``split`` keys (a multiple of 64) per chunk,
+    counted from the first seen key rounded down to a block of 64; ``chunks`` chunks cover the most keys any token sees."""
+    __slots__ = ("split", "chunks")
+
+    def __init__(self, split: int, chunks: int):
+        self.split, self.chunks = int(split), int(chunks)
 
 
 def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span: int, window: int, chunk: int):
-    """What single-token steps fix ahead (the plain kernel needs nothing)."""
-    return None
+    """Enough chunks for about four CTAs per SM over all requests and kv heads, none shorter than 64 keys.  A token sees at
+    most its window or its chunk of keys, whatever the sequence's length: the split follows that, not the context.  None
+    where the plain kernel runs (it needs no plan)."""
+    if not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv)):
+        return None
+    seen = max(int(span), 1)
+    if window > 0:
+        seen = min(seen, window)
+    if chunk > 0:
+        seen = min(seen, chunk)
+    longest = seen + 63                                # the first chunk starts on a block border at or before the first seen key
+    want = max(1, -(-4 * SM_COUNT // max(1, requests * K)))
+    split = max(64, -(-(-(-longest // want)) // 64) * 64)
+    return SinkDecodePlan(split, max(1, -(-longest // split)))
 
 
 # ---- routed feed-forward ------------------------------------------------------------------------------------------------------
@@ -1281,6 +1352,15 @@ def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Te
     launches_extra(1)
 
 
+#: bf16 experts go to the grouped tensor-core kernels where the sizes allow (False: always the plain kernels)
+use_fast_experts = True
+
+
+def fast_experts_supported(h: int, ff: int) -> bool:
+    """Both inner sizes of the experts' products in whole steps of 64 (the grouped kernel's k-step)."""
+    return h % 64 == 0 and ff % 64 == 0
+
+
 def moe_jobs(dtype, h: int, ff: int) -> dict:
     return library_jobs("mb_moe")
 
@@ -1289,6 +1369,25 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
                 y: torch.Tensor, weight_on_input: bool, workspace) -> None:
     """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``."""
     T, top = experts.shape
-    ff = w_down.shape[2]
-    act = workspace.get("moe_act", (T * top, ff), x.dtype)
-    moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input)
+    E, h, ff = w_down.shape
+    pairs = T * top
+    act = workspace.get("moe_act", (pairs, ff), x.dtype)
+    if not (use_fast_experts and x.dtype == torch.bfloat16 and fast_experts_supported(h, ff)):
+        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input)
+        return
+    _need_cuda(x, w_gate_up, w_down, experts, weights, y)
+    assert tuple(w_gate_up.shape) == (E, 2 * ff, h) and w_gate_up.dtype == w_down.dtype == x.dtype and tuple(y.shape) == (T, h)
+    assert y.dtype == torch.float32 and experts.dtype == torch.int32 and weights.dtype == torch.float32
+    ints = workspace.get("moe_ints", (E + 1 + 3 * pairs,), torch.int32)
+    offsets, order, inv, token_sorted = ints[:E + 1], ints[E + 1:E + 1 + pairs], ints[E + 1 + pairs:E + 1 + 2 * pairs], ints[E + 1 + 2 * pairs:]
+    weight_sorted = workspace.get("moe_weight_sorted", (pairs,), torch.float32)
+    xs = workspace.get("moe_xs", (pairs, h), x.dtype)
+    rows = workspace.get("moe_rows", (pairs, h), torch.float32) if top > 1 else None
+    size = x.element_size()
+    _cost(min(pairs, E) * 3 * ff * h * size + 3 * pairs * h * size + 2 * pairs * ff * size + 2 * _size(y) + (2 * _size(rows) if rows is not None else 0),
+          6.0 * pairs * ff * h)
+    _check(_lib("mb_moe").mb_moe_experts_fast(
+        _ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(offsets), _ptr(order), _ptr(inv), _ptr(token_sorted),
+        _ptr(weight_sorted), _ptr(xs), _ptr(act), _ptr(rows), _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(E), _c_int(top),
+        _c_int(int(weight_on_input)), _stream()), "experts (grouped, tensor cores)")
+    launches_extra(3 if top == 1 else 4)

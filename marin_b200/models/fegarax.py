@@ -63,7 +63,9 @@ def build_spec(cfg: FegaraxConfig) -> ModelSpec:
         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "name": "head", "tied": True}),
         layers=layers,
         schedule=[ScheduleEntry(i) for i in range(len(cfg.layers))],
-        streams=cfg.streams if cfg.streams is not None else 1,
+        streams=cfg.streams if cfg.streams is not None else 0,
+        # a layer outside the value mixing has no use for a mixing number, should a checkpoint bring one
+        ignorable=tuple(f"l{i}.mix.vmix" for i, layer in enumerate(cfg.layers) if not layer.mixer["v_mix"]),
     )
 
 

@@ -121,7 +121,7 @@ class Model:
         T = ctx.num_tokens
         S = self.spec.streams
         ops.stage_name = "embedding"
-        if S > 1:
+        if S > 0:
             # several copies of the residual stream, all equal to the embedding's output at first
             hidden = ws.get("hidden", (S, T, self.spec.hidden_size), torch.float32)
             self.embedding.forward(ctx.token_ids, hidden[0], ctx.positions)
@@ -154,7 +154,7 @@ class Model:
             return torch.empty(0, self.spec.vocab_size, device=rt.device, dtype=torch.float32)
         ops.stage_name = "final norm"
         rows = ws.get("logit_hidden", (W, self.spec.hidden_size), torch.float32)
-        if S > 1:
+        if S > 0:
             ops.hc_sum(hidden, ctx.logit_rows, rows)
         else:
             ops.gather_rows(hidden, ctx.logit_rows, rows)

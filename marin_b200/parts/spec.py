@@ -72,6 +72,6 @@ class ModelSpec:
     schedule: List[ScheduleEntry]
     #: tensors that may be present in a checkpoint and are ignored (e.g. an unused head when tied)
     ignorable: Tuple[str, ...] = ()
-    #: how many copies of the residual stream the blocks keep (hyper-connections); the model hands its blocks a float32
-    #: ``[streams, T, hidden]`` tensor when there are more than one, and the head reads their sum
-    streams: int = 1
+    #: how many copies of the residual stream the blocks keep (hyper-connections): the model then hands its blocks a float32
+    #: ``[streams, T, hidden]`` tensor (also for a single copy) and the head reads their sum; 0: one plain ``[T, hidden]`` stream
+    streams: int = 0

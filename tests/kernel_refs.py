@@ -13,8 +13,10 @@ from contextlib import contextmanager
 import torch
 
 
-def embed(ids, table, out):
-    out.copy_(table[ids.long()].float())
+def embed(ids, table, out, pos_table=None, positions=None, scale=1.0):
+    out.copy_(table[ids.long()].float() * scale)
+    if pos_table is not None:
+        out.add_(pos_table[positions.long()].float())
 
 
 def rmsnorm(x, weight, eps, out, unit_offset=False):

@@ -74,18 +74,20 @@ def visible(T: int, mask: Optional[dict]) -> torch.Tensor:
     return see
 
 
-def sink_softmax_mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[dict]) -> torch.Tensor:
+def sink_softmax_mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[dict], sink: bool = True) -> torch.Tensor:
     """One head.  ``q`` ``[T, d]``, ``k`` ``[T, d]``, ``v`` ``[T, dv]``.  Weights ``exp(s_j) / (1 + sum_j exp(s_j))`` over the keys a
-    position sees: the one stands for a key of score 0 that has no value."""
+    position sees: the one stands for a key of score 0 that has no value (``sink=False``: an ordinary softmax)."""
     s = (q @ k.T) * scale
     s = s.masked_fill(~visible(q.shape[0], mask), -math.inf)
-    m = torch.clamp(s.max(dim=-1, keepdim=True).values, min=0.0)
+    m = s.max(dim=-1, keepdim=True).values
+    if sink:
+        m = torch.clamp(m, min=0.0)
     e = torch.exp(s - m)
-    return (e @ v) / (torch.exp(-m) + e.sum(dim=-1, keepdim=True))
+    return (e @ v) / ((torch.exp(-m) if sink else 0.0) + e.sum(dim=-1, keepdim=True))
 
 
 def attention_mixer(h: torch.Tensor, positions: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, m: dict, eps: float,
-                    shared: dict, first_vmix: bool) -> torch.Tensor:
+                    shared: dict, first_vmix: bool, sink: bool = True) -> torch.Tensor:
     """The attention mixer over a whole sequence.  ``shared['v_first']`` carries the values of the first value-mixing layer."""
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
@@ -106,29 +108,58 @@ def attention_mixer(h: torch.Tensor, positions: torch.Tensor, W: Dict[str, torch
     heads = []
     for hh in range(H):
         g = hh // (H // G)
-        heads.append(sink_softmax_mix(q[:, hh], k[:, g], v[:, g], float(m["scale"]), m.get("mask")))
+        heads.append(sink_softmax_mix(q[:, hh], k[:, g], v[:, g], float(m["scale"]), m.get("mask"), sink))
     o = torch.cat(heads, dim=-1)
     o = o * torch.sigmoid(h @ f64(W[pre + "g"]).T)
     return o @ f64(W[pre + "o"]).T
 
 
-def routed_experts(h: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, mlp: dict) -> torch.Tensor:
-    """Sigmoid scores, the ``top`` largest chosen, each chosen expert fed ``score * h``; outputs summed."""
+def router_margins(h: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, mlp: dict) -> torch.Tensor:
+    """Per token, how far the last chosen expert's router logit lies above the best one left out (inf if none is left out)."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    s = torch.sigmoid(h @ f64(W[pre + "router"]).T)
+    z = (h @ f64(W[pre + "router"]).T).sort(dim=-1, descending=True).values
+    return z[:, top - 1] - z[:, top] if top < E else torch.full((h.shape[0],), math.inf, dtype=F64)
+
+
+def routed_experts(h: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, mlp: dict, score: str = "sigmoid", renormalize: bool = False,
+                   weight_on: str = "input") -> torch.Tensor:
+    """Sigmoid scores, the ``top`` largest chosen, each chosen expert fed ``score * h``; outputs summed.  (The other settings
+    of the part: scores from a softmax over all experts, weights renormalised over the chosen ones, the weight on the output.)"""
+    E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+    z = h @ f64(W[pre + "router"]).T
+    s = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
+        order = sorted(range(E), key=lambda e: (-float(z[t, e]), e))[:top]
+        total = sum(float(s[t, e]) for e in order) if renormalize else 1.0
         for e in order:
-            x = s[t, e] * h[t]
+            w = s[t, e] / total
+            x = w * h[t] if weight_on == "input" else h[t]
             gate = f64(W[f"{pre}e{e}.gate"]) @ x
             up = f64(W[f"{pre}e{e}.up"]) @ x
-            out[t] += f64(W[f"{pre}e{e}.down"]) @ (gate * torch.sigmoid(gate) * up)
+            y = f64(W[f"{pre}e{e}.down"]) @ (gate * torch.sigmoid(gate) * up)
+            out[t] += y if weight_on == "input" else w * y
     return out
 
 
-def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int]):
-    """Logits ``[T, vocab]`` and the residual stream after every layer ``[layers, T, width]`` (the sum of the streams)."""
+def hyper_step(streams: List[torch.Tensor], w_in, w_out, w_mix, fn):
+    """One sublayer over the streams: ``u = sum_s in[s] x_s``, ``y = fn(u)``, ``x_t <- sum_s mix[s, t] x_s + out[t] y``."""
+    n = len(streams)
+    u = sum(w_in[s] * streams[s] for s in range(n))
+    y = fn(u)
+    return [sum(w_mix[s, t] * streams[s] for s in range(n)) + w_out[t] * y for t in range(n)]
+
+
+def read_weights(model_dir: str) -> Dict[str, torch.Tensor]:
+    from safetensors.torch import load_file
+    import os
+
+    return load_file(os.path.join(model_dir, "model.safetensors"))
+
+
+def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], margins: Optional[list] = None):
+    """Logits ``[T, vocab]`` and the residual stream after every layer ``[layers, T, width]`` (the sum of the streams).
+    ``margins`` collects every routed layer's ``router_margins``."""
     eps = float(cfg["norm"]["eps"])
     T = len(tokens)
     positions = torch.arange(T)
@@ -150,14 +181,17 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int]):
             return y
 
         subs = [(1, mixer)]
+        def experts(hh):
+            if margins is not None:
+                margins.append(router_margins(hh, W, pre + "mlp.", layer["mlp"]))
+            return routed_experts(hh, W, pre + "mlp.", layer["mlp"])
+
         if layer.get("mlp") is not None:
-            subs.append((2, lambda hh: routed_experts(hh, W, pre + "mlp.", layer["mlp"])))
+            subs.append((2, experts))
         for qn, fn in subs:
             if S:
-                w_in, w_out, w_mix = f64(W[f"{pre}hc{qn}.in"]), f64(W[f"{pre}hc{qn}.out"]), f64(W[f"{pre}hc{qn}.mix"])
-                u = sum(w_in[s] * streams[s] for s in range(len(streams)))
-                y = fn(rms_norm(u, W[f"{pre}norm{qn}"], eps, True))
-                streams = [sum(w_mix[s, t] * streams[s] for s in range(len(streams))) + w_out[t] * y for t in range(len(streams))]
+                streams = hyper_step(streams, f64(W[f"{pre}hc{qn}.in"]), f64(W[f"{pre}hc{qn}.out"]), f64(W[f"{pre}hc{qn}.mix"]),
+                                     lambda u: fn(rms_norm(u, W[f"{pre}norm{qn}"], eps, True)))
             else:
                 streams[0] = streams[0] + fn(rms_norm(streams[0], W[f"{pre}norm{qn}"], eps, True))
         after.append(sum(streams))
