@@ -52,19 +52,19 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
             cs_tab[half + i] = sn * rot_mag;
         }
     }
-    // a warp per head: load (+ bias), sum of squares in lane order then across lanes
+    // every element of q and k (+ bias) into shared memory as float32, all threads side by side
+    const int qk = heads * d, q_len = H * d;
+    for (int idx = threadIdx.x; idx < qk; idx += QF_THREADS) {
+        float v = to_f32(src[idx]);
+        if (idx < q_len) { if (q_b != nullptr) v += q_b[idx]; }
+        else if (k_b != nullptr) v += k_b[idx - q_len];
+        vals[idx] = v;
+    }
+    __syncthreads();
+    // sums of squares per head: a warp per head, lanes in a fixed order
     for (int head = warp; head < heads; head += warps) {
-        const bool is_q = head < H;
-        const float* bias = is_q ? q_b : k_b;
-        const int col0 = head * d;                                  // q and k lie side by side in the row
-        const int b0 = is_q ? col0 : col0 - H * d;
         float ss = 0.0f;
-        for (int i = lane; i < d; i += 32) {
-            float v = to_f32(src[col0 + i]);
-            if (bias != nullptr) v += bias[b0 + i];
-            vals[col0 + i] = v;
-            ss += v * v;
-        }
+        for (int i = lane; i < d; i += 32) { const float v = vals[head * d + i]; ss += v * v; }
         ss = warp_sum(ss);
         if (lane == 0) head_ss[head] = ss;
     }
@@ -77,10 +77,12 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
     }
     __syncthreads();
     const int slot = write_kv ? slot_mapping[t] : -1;
-    for (int head = warp; head < heads; head += warps) {
+    T* k_dst = slot >= 0 ? k_cache + (((size_t)(slot / page_size)) * K * page_size + (size_t)(slot % page_size)) * d : nullptr;
+    for (int idx = threadIdx.x; idx < qk; idx += QF_THREADS) {
+        const int head = idx / d, i = idx - head * d;
         const bool is_q = head < H;
-        const int col0 = head * d;
         const int kh = head - H;
+        if (!is_q && k_dst == nullptr) continue;
         float factor = 1.0f;
         const float* w = nullptr;
         if (norm_mode == 1) {
@@ -88,23 +90,18 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
             w = is_q ? q_w : k_w;
         } else if (norm_mode == 2) {
             factor = s_factor[is_q ? 0 : 1];
-            w = is_q ? q_w + col0 : k_w + (size_t)kh * d;
+            w = is_q ? q_w + (size_t)head * d : k_w + (size_t)kh * d;
         }
-        T* dst = nullptr;
-        if (is_q) dst = q_out + ((size_t)t * H + head) * d;
-        else if (slot >= 0) dst = k_cache + ((((size_t)(slot / page_size)) * K + kh) * page_size + (size_t)(slot % page_size)) * d;
-        if (dst == nullptr) continue;
-        for (int i = lane; i < d; i += 32) {
-            float a = vals[col0 + i] * factor * (w != nullptr ? w[i] : 1.0f);
-            if (inv_freq != nullptr && i < rot_dim) {
-                const bool low = i < half;
-                const int j = low ? i : i - half, other = low ? i + half : i - half;
-                const float b = vals[col0 + other] * factor * (w != nullptr ? w[other] : 1.0f);
-                const float cs = cs_tab[j], sn = cs_tab[half + j];
-                a = low ? a * cs - b * sn : a * cs + b * sn;
-            }
-            dst[i] = from_f32<T>(a);
+        float a = vals[idx] * factor * (w != nullptr ? w[i] : 1.0f);
+        if (inv_freq != nullptr && i < rot_dim) {
+            const bool low = i < half;
+            const int j = low ? i : i - half, other = low ? i + half : i - half;
+            const float b = vals[head * d + other] * factor * (w != nullptr ? w[other] : 1.0f);
+            const float cs = cs_tab[j], sn = cs_tab[half + j];
+            a = low ? a * cs - b * sn : a * cs + b * sn;
         }
+        if (is_q) q_out[(size_t)t * q_len + idx] = from_f32<T>(a);
+        else k_dst[(size_t)kh * page_size * d + i] = from_f32<T>(a);
     }
     if (!write_kv) return;
     const float lam = v_mode == 2 ? *v_lambda : 0.0f;

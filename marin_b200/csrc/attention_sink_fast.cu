@@ -355,32 +355,49 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     }
 }
 
-// out[r][h][:] = (sum_c acc_c 2^(m_c - M)) / (sink 2^(-M) + sum_c l_c 2^(m_c - M)) * sigmoid(gate), chunks in increasing order
-__global__ void attn_sink_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, const int* __restrict__ seq_lens,
-                                       int split, int window, int chunk_size, int sink, int R, int H, const bf16* __restrict__ gate,
-                                       int gate_stride, bf16* __restrict__ out) {
+// out[r][h][:] = (sum_c acc_c 2^(m_c - M)) / (sink 2^(-M) + sum_c l_c 2^(m_c - M)) * sigmoid(gate), chunks in increasing order.
+// A block per (request, head): the chunks' weights 2^(m_c - M) are made side by side, then every output is one sum over the chunks.
+#define MG_THREADS 128
+#define MG_MAX_CHUNKS 1024
+__global__ void __launch_bounds__(MG_THREADS) attn_sink_merge_kernel(
+    const float* __restrict__ part_acc, const float* __restrict__ part_ml, const int* __restrict__ seq_lens, int split, int window,
+    int chunk_size, int sink, int R, int H, const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out) {
     PDL_ENTER();
     part_acc = pdl_fresh(part_acc); part_ml = pdl_fresh(part_ml); gate = pdl_fresh(gate);
+    __shared__ float wgt[MG_MAX_CHUNKS], scratch[32];
     const int r = blockIdx.x / H, h = blockIdx.x % H;
     const int len = seq_lens[r];
     if (len <= 0) return;
     const int pos = len - 1;
     const int start = (first_seen(pos, window, chunk_size) / BN) * BN;
-    const int chunks = (len - start + split - 1) / split;
-    float M = sink ? 0.0f : -INFINITY;
-    for (int c = 0; c < chunks; ++c) M = fmaxf(M, part_ml[(((size_t)c * R + r) * H + h) * 2]);
-    float total = sink ? exp2f(-M) : 0.0f;
-    for (int c = 0; c < chunks; ++c) {
+    const int chunks = min((len - start + split - 1) / split, MG_MAX_CHUNKS);
+    float mx = sink ? 0.0f : -INFINITY;
+    for (int c = threadIdx.x; c < chunks; c += MG_THREADS) {
         const float mc = part_ml[(((size_t)c * R + r) * H + h) * 2];
-        if (mc != -INFINITY) total = fmaf(part_ml[(((size_t)c * R + r) * H + h) * 2 + 1], exp2f(mc - M), total);
+        wgt[c] = mc;
+        mx = fmaxf(mx, mc);
     }
+    const float M = block_max(mx, scratch);
+    float part = 0.0f;
+    for (int c = threadIdx.x; c < chunks; c += MG_THREADS) {
+        const float mc = wgt[c];
+        const float f = mc == -INFINITY ? 0.0f : exp2f(mc - M);
+        wgt[c] = f;
+        part = fmaf(part_ml[(((size_t)c * R + r) * H + h) * 2 + 1], f, part);
+    }
+    const float total = block_sum(part, scratch) + (sink ? exp2f(-M) : 0.0f);       // (its barriers publish wgt)
     const float inv = 1.0f / total;
-    for (int i = threadIdx.x; i < DV; i += blockDim.x) {
+    for (int i = threadIdx.x; i < DV; i += MG_THREADS) {
         float a = 0.0f;
-        for (int c = 0; c < chunks; ++c) {
-            const float mc = part_ml[(((size_t)c * R + r) * H + h) * 2];
-            if (mc != -INFINITY) a = fmaf(part_acc[(((size_t)c * R + r) * H + h) * DV + i], exp2f(mc - M), a);
+        int c = 0;
+        for (; c + 8 <= chunks; c += 8) {                      // eight loads in flight, added in chunk order
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = part_acc[(((size_t)(c + u) * R + r) * H + h) * DV + i];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a = fmaf(x[u], wgt[c + u], a);
         }
+        for (; c < chunks; ++c) a = fmaf(part_acc[(((size_t)c * R + r) * H + h) * DV + i], wgt[c], a);
         a *= inv;
         if (gate != nullptr) a *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_stride + (size_t)h * DV + i])));
         out[((size_t)r * H + h) * DV + i] = __float2bfloat16_rn(a);
@@ -397,19 +414,24 @@ MB_API int mb_attn_sink_layout(int* d, int* dv, int* group) { *d = D; *dv = DV; 
 
 // Single tokens: requests 0 .. requests - 1 bring one token each (token t belongs to request t).  part_acc: float32
 // [chunks][requests][K * GROUP][V_DIM], part_ml: [chunks][requests][K * GROUP][2]; split: keys per chunk, a multiple of 64;
-// chunks * split covers the most keys a token sees plus one block.  The second kernel writes out (bf16 [requests][H][V_DIM]).
-MB_API int mb_attn_sink_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
+// chunks * split covers the most keys a token sees plus one block.
+MB_API int mb_attn_sink_decode(const void* q, const void* k_cache, const void* v_cache, float* part_acc, float* part_ml,
                                const int* block_table, int max_pages, const int* seq_lens, int requests, int K, int page_size,
-                               float scale, int window, int chunk, int sink, const void* gate, int gate_stride, int split, int chunks,
-                               cudaStream_t s) {
+                               float scale, int window, int chunk, int split, int chunks, cudaStream_t s) {
     if (requests <= 0) return 0;
     const int shift = page_shift_of(page_size);
-    if (shift < 0 || split <= 0 || split % BN != 0 || chunks <= 0 || window < 0 || chunk < 0) return MB_ERR_BAD_SIZE;
+    if (shift < 0 || split <= 0 || split % BN != 0 || chunks <= 0 || chunks > MG_MAX_CHUNKS || window < 0 || chunk < 0) return MB_ERR_BAD_SIZE;
     cudaFuncSetAttribute(attn_sink_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
-    const int rc = launch_kernel(attn_sink_decode_kernel, dim3(chunks, K, requests), 128, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
-                                 (const bf16*)v_cache, part_acc, part_ml, block_table, max_pages, seq_lens, K, shift, scale, window, chunk, split);
-    if (rc != 0) return rc;
-    return launch_kernel(attn_sink_merge_kernel, requests * K * GROUP, DV >= 64 ? 64 : 32, 0, s, 0, (const float*)part_acc,
+    return launch_kernel(attn_sink_decode_kernel, dim3(chunks, K, requests), 128, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
+                         (const bf16*)v_cache, part_acc, part_ml, block_table, max_pages, seq_lens, K, shift, scale, window, chunk, split);
+}
+
+// The parts of every request merged in chunk order, with the sink and the gate: out bf16 [requests][K * GROUP][V_DIM].
+MB_API int mb_attn_sink_merge(const float* part_acc, const float* part_ml, void* out, const int* seq_lens, int requests, int K, int window,
+                              int chunk, int sink, const void* gate, int gate_stride, int split, cudaStream_t s) {
+    if (requests <= 0) return 0;
+    if (split <= 0) return MB_ERR_BAD_SIZE;
+    return launch_kernel(attn_sink_merge_kernel, requests * K * GROUP, MG_THREADS, 0, s, 0, (const float*)part_acc,
                          (const float*)part_ml, seq_lens, split, window, chunk, sink, requests, K * GROUP, (const bf16*)gate, gate_stride,
                          (bf16*)out);
 }

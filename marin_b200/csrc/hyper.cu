@@ -12,11 +12,12 @@
 
 #define HC_MAX_STREAMS 8
 #define HC_THREADS 256
+#define HC_MAX_THREADS 1024        // few tokens: a row is spread over more threads, the loads of a row are all in flight at once
 
 // mix, w_out, y null: no write.  w_in null: no read (norm_w, out unused).  y (float32 [tokens][h]) is zeroed after it
 // was read, so that the next sublayer can add its output into it.
 template <typename TO, int S>
-__global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(float* __restrict__ streams, int tokens, int h,
+__global__ void __launch_bounds__(HC_MAX_THREADS) hc_step_kernel(float* __restrict__ streams, int tokens, int h,
                                                              const float* __restrict__ mix, const float* __restrict__ w_out,
                                                              float* __restrict__ y, const float* __restrict__ w_in,
                                                              const float* __restrict__ norm_w, float eps, int unit_offset,
@@ -35,7 +36,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(float* __restrict__
     const size_t t = blockIdx.x;
     const size_t plane = (size_t)tokens * h;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < h; i += HC_THREADS) {
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
         float x[S];
 #pragma unroll
         for (int s = 0; s < S; ++s) x[s] = streams[s * plane + t * h + i];
@@ -64,7 +65,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(float* __restrict__
     if (w_in == nullptr) return;
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)h + eps);
-    for (int i = threadIdx.x; i < h; i += HC_THREADS) {
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
         const float wi = unit_offset ? 1.0f + norm_w[i] : norm_w[i];
         out[t * h + i] = from_f32<TO>(u_row[i] * scale * wi);
     }
@@ -78,7 +79,10 @@ static int hc_launch(float* streams, int tokens, int h, const float* mix, const 
         const int rc = (int)cudaFuncSetAttribute(hc_step_kernel<TO, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (rc != 0) return rc;
     }
-    return launch_kernel(hc_step_kernel<TO, S>, tokens, HC_THREADS, smem, s, 0, streams, tokens, h, mix, w_out, y, w_in, norm_w, eps,
+    int threads = HC_THREADS;
+    // (only where rows leave as bf16: in true float32 a row's sum of squares is added in the same order whatever the batch holds)
+    if (tokens <= 64 && sizeof(TO) == 2) while (threads < HC_MAX_THREADS && threads * 2 <= h) threads *= 2;
+    return launch_kernel(hc_step_kernel<TO, S>, tokens, threads, smem, s, 0, streams, tokens, h, mix, w_out, y, w_in, norm_w, eps,
                          unit_offset, (TO*)out);
 }
 

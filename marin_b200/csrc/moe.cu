@@ -6,37 +6,53 @@
 // Kernels: the router with its top-k (a warp per token), the grouping of (token, choice) pairs by expert (offsets and an
 // order), and the plain expert products for any size in both dtypes (a pair per block).  A pair's result never depends on
 // which other pairs the step holds or on the order they were grouped in; a token's pairs are added in choice order.
-// Weights: gate|up as [experts][2 ff][h] (gate rows first), down as [experts][h][ff].
+// Weights: gate|up as [experts][2 ff][h], down as [experts][h][ff].  The gate and up rows of an expert lie either one after
+// the other (gate rows first) or, `interleaved`, in alternating blocks of 16 rows (16 gate rows, the 16 up rows of the same
+// columns, ...): the layout the dense product's fused SwiGLU epilogue reads, so that an expert's matrix can go to it as it is.
 #define MB_LIB "moe"
 #define MB_LIB_ID 14
 #include "common.cuh"
 #include "launch.cuh"
 
-#define MR_WARPS 4
+#define MR_THREADS 256
 
-// ---- router and top-k: a warp per token -------------------------------------------------------------------------------
+// Row of gate column c (which = 0) or up column c (which = 1) in an expert's gate|up matrix.
+__host__ __device__ __forceinline__ int gate_up_row(int c, int which, int ff, int interleaved) {
+    return interleaved ? (c / 16) * 32 + which * 16 + c % 16 : which * ff + c;
+}
+
+// ---- router and top-k: a token per block -------------------------------------------------------------------------------
 // expert_out int32 [tokens][top], weight_out float32 [tokens][top], choices in order of decreasing score (the lower expert
-// among equals).  score_mode 0: sigmoid, 1: softmax over all experts.
+// among equals).  score_mode 0: sigmoid, 1: softmax over all experts.  A warp takes every eighth expert; its lanes walk the
+// row in a fixed order, so a token's logits do not depend on the batch.
 template <typename T>
-__global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const T* __restrict__ h_rows, const float* __restrict__ router,
-                                                                  int* __restrict__ expert_out, float* __restrict__ weight_out,
-                                                                  int tokens, int h, int E, int top, int score_mode, int renorm) {
+__global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restrict__ h_rows, const float* __restrict__ router,
+                                                               int* __restrict__ expert_out, float* __restrict__ weight_out,
+                                                               int tokens, int h, int E, int top, int score_mode, int renorm) {
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows);
     extern __shared__ float smem[];
+    float* z = smem;                           // [E]
+    float* xrow = smem + E;                    // [h]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* z = smem + (size_t)warp * E;
-    const int t = blockIdx.x * MR_WARPS + warp;
-    if (t >= tokens) return;
+    const int t = blockIdx.x;
     const T* x = h_rows + (size_t)t * h;
-    for (int e = 0; e < E; ++e) {
+    for (int i = threadIdx.x; i < h; i += MR_THREADS) xrow[i] = to_f32(x[i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += MR_THREADS / 32) {
         const float* w = router + (size_t)e * h;
-        float dot = 0.0f;
-        for (int i = lane; i < h; i += 32) dot = fmaf(to_f32(x[i]), w[i], dot);
-        dot = warp_sum(dot);
+        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+        int i = lane;
+        for (; i + 96 < h; i += 128) {
+            d0 = fmaf(xrow[i], w[i], d0); d1 = fmaf(xrow[i + 32], w[i + 32], d1);
+            d2 = fmaf(xrow[i + 64], w[i + 64], d2); d3 = fmaf(xrow[i + 96], w[i + 96], d3);
+        }
+        for (; i < h; i += 32) d0 = fmaf(xrow[i], w[i], d0);
+        const float dot = warp_sum((d0 + d1) + (d2 + d3));
         if (lane == 0) z[e] = dot;
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float denom = 1.0f, zmax = 0.0f;
     if (score_mode == 1) {
         float mx = -INFINITY;
@@ -78,14 +94,13 @@ MB_API int mb_moe_route(const void* h_rows, int dtype, const float* router, int*
                         int E, int top, int score_mode, int renorm, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || h <= 0 || score_mode < 0 || score_mode > 1) return MB_ERR_BAD_SIZE;
-    const size_t smem = (size_t)MR_WARPS * E * sizeof(float);
+    const size_t smem = (size_t)(E + h) * sizeof(float);
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
-    const int blocks = (tokens + MR_WARPS - 1) / MR_WARPS;
     if (dtype == MB_F32)
-        return launch_kernel(moe_route_kernel<float>, blocks, MR_WARPS * 32, smem, s, 0, (const float*)h_rows, router, expert_out,
+        return launch_kernel(moe_route_kernel<float>, tokens, MR_THREADS, smem, s, 0, (const float*)h_rows, router, expert_out,
                              weight_out, tokens, h, E, top, score_mode, renorm);
     if (dtype == MB_BF16)
-        return launch_kernel(moe_route_kernel<bf16>, blocks, MR_WARPS * 32, smem, s, 0, (const bf16*)h_rows, router, expert_out,
+        return launch_kernel(moe_route_kernel<bf16>, tokens, MR_THREADS, smem, s, 0, (const bf16*)h_rows, router, expert_out,
                              weight_out, tokens, h, E, top, score_mode, renorm);
     return MB_ERR_BAD_DTYPE;
 }
@@ -125,7 +140,8 @@ MB_API int mb_moe_group(const int* expert_of, int pairs, int E, int* offsets, in
 template <typename T>
 __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __restrict__ h_rows, const T* __restrict__ w_gate_up,
                                                                  const int* __restrict__ expert_of, const float* __restrict__ weight_of,
-                                                                 T* __restrict__ act, int h, int ff, int top, int weight_on_input) {
+                                                                 T* __restrict__ act, int h, int ff, int top, int weight_on_input,
+                                                                 int interleaved) {
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows); expert_of = pdl_fresh(expert_of); weight_of = pdl_fresh(weight_of);
     extern __shared__ float x[];               // [h]
@@ -138,8 +154,8 @@ __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __rest
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* base = w_gate_up + (size_t)e * 2 * ff * h;
     for (int c = warp; c < ff; c += ME_THREADS / 32) {
-        const T* g = base + (size_t)c * h;
-        const T* u = base + (size_t)(ff + c) * h;
+        const T* g = base + (size_t)gate_up_row(c, 0, ff, interleaved) * h;
+        const T* u = base + (size_t)gate_up_row(c, 1, ff, interleaved) * h;
         float dg = 0.0f, du = 0.0f;
         for (int i = lane; i < h; i += 32) { dg = fmaf(x[i], to_f32(g[i]), dg); du = fmaf(x[i], to_f32(u[i]), du); }
         dg = warp_sum(dg);
@@ -177,23 +193,23 @@ __global__ void __launch_bounds__(ME_THREADS) moe_down_kernel(const T* __restric
     }
 }
 
+// which = 0: act <- the activations of every pair; which = 1: y += the chosen experts' outputs, from act.
 MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gate_up, const void* w_down, const int* expert_of,
                                 const float* weight_of, void* act, float* y, int tokens, int h, int ff, int top, int weight_on_input,
-                                cudaStream_t s) {
+                                int interleaved, int which, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (h <= 0 || ff <= 0 || top <= 0 || (size_t)h * 4 > 48 * 1024 || (size_t)ff * 4 > 48 * 1024) return MB_ERR_BAD_SIZE;
-    int rc;
     if (dtype == MB_F32) {
-        rc = launch_kernel(moe_gate_up_kernel<float>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const float*)h_rows,
-                           (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input);
-        if (rc != 0) return rc;
+        if (which == 0)
+            return launch_kernel(moe_gate_up_kernel<float>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const float*)h_rows,
+                                 (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input, interleaved);
         return launch_kernel(moe_down_kernel<float>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const float*)act, (const float*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
     if (dtype == MB_BF16) {
-        rc = launch_kernel(moe_gate_up_kernel<bf16>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const bf16*)h_rows,
-                           (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input);
-        if (rc != 0) return rc;
+        if (which == 0)
+            return launch_kernel(moe_gate_up_kernel<bf16>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const bf16*)h_rows,
+                                 (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input, interleaved);
         return launch_kernel(moe_down_kernel<bf16>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const bf16*)act, (const bf16*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
@@ -214,7 +230,9 @@ MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gat
 #define GN 64
 #define GK 64
 #define GLD (GK + 8)
-#define G_STAGES 3
+// stages of the cp.async ring: the down product has one weight tile per stage and few CTAs when few experts are chosen, so it
+// keeps more stages in flight
+#define G_STAGES_OF(MODE) ((MODE) == 0 ? 4 : 6)
 
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h_rows, const int* __restrict__ order, const float* __restrict__ weight_of,
@@ -237,10 +255,11 @@ template <int MODE>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
                                                           const int* __restrict__ offsets, int E, int N, int K, bf16* __restrict__ act_out,
                                                           float* __restrict__ f_out, const int* __restrict__ dst_rows,
-                                                          const float* __restrict__ row_scale, int accumulate) {
+                                                          const float* __restrict__ row_scale, int accumulate, int interleaved) {
     PDL_ENTER();
     A = pdl_fresh(A); offsets = pdl_fresh(offsets); dst_rows = pdl_fresh(dst_rows); row_scale = pdl_fresh(row_scale); f_out = pdl_fresh(f_out);
     constexpr int NB = MODE == 0 ? 2 : 1;
+    constexpr int G_STAGES = G_STAGES_OF(MODE);
     extern __shared__ __align__(16) uint8_t g_smem[];
     bf16* sA = reinterpret_cast<bf16*>(g_smem);                              // [G_STAGES][GM][GLD]
     bf16* sB = sA + G_STAGES * GM * GLD;                                     // [G_STAGES][NB][GN][GLD]
@@ -256,23 +275,31 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
     const int col0 = blockIdx.y * GN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bf16* We = W + (size_t)e * NB * N * K;
+    const int a_rows = min(GM, row_end - row0), b_rows = min(GN, N - col0);
+    // rows of a tile past the expert's pairs, or past the last column, are zero in every stage and are never copied into
+    for (int idx = threadIdx.x; idx < G_STAGES * GM * (GK / 8); idx += 128) {
+        const int r = (idx / (GK / 8)) % GM;
+        if (r >= a_rows) *reinterpret_cast<uint4*>(sA + (idx / (GK / 8)) * GLD + (idx % (GK / 8)) * 8) = make_uint4(0, 0, 0, 0);
+    }
+    if (b_rows < GN)
+        for (int idx = threadIdx.x; idx < G_STAGES * NB * GN * (GK / 8); idx += 128) {
+            const int r = (idx / (GK / 8)) % GN;
+            if (r >= b_rows) *reinterpret_cast<uint4*>(sB + (idx / (GK / 8)) * GLD + (idx % (GK / 8)) * 8) = make_uint4(0, 0, 0, 0);
+        }
     auto load = [&](int stage, int kt) {
         const int k0 = kt * GK;
         bf16* a = sA + stage * GM * GLD;
-        for (int idx = threadIdx.x; idx < GM * (GK / 8); idx += 128) {
+        for (int idx = threadIdx.x; idx < a_rows * (GK / 8); idx += 128) {
             const int r = idx / (GK / 8), c = idx % (GK / 8);
-            bf16* dst = a + r * GLD + c * 8;
-            if (row0 + r < row_end) cp_async16(dst, A + (size_t)(row0 + r) * K + k0 + c * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            cp_async16(a + r * GLD + c * 8, A + (size_t)(row0 + r) * K + k0 + c * 8);
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             bf16* b = sB + (stage * NB + nb) * GN * GLD;
-            for (int idx = threadIdx.x; idx < GN * (GK / 8); idx += 128) {
+            for (int idx = threadIdx.x; idx < b_rows * (GK / 8); idx += 128) {
                 const int r = idx / (GK / 8), c = idx % (GK / 8);
-                bf16* dst = b + r * GLD + c * 8;
-                if (col0 + r < N) cp_async16(dst, We + ((size_t)nb * N + col0 + r) * K + k0 + c * 8);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                const int wrow = MODE == 0 ? gate_up_row(col0 + r, nb, N, interleaved) : col0 + r;
+                cp_async16(b + r * GLD + c * 8, We + (size_t)wrow * K + k0 + c * 8);
             }
         }
     };
@@ -345,47 +372,60 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
     }
 }
 
-// y[t][c] += sum over the token's choices, in choice order, of rows[inv[t top + choice]][c]
-__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ inv, float* __restrict__ y, int h, int top) {
+// y[t][c] += sum over the token's choices, in choice order, of rows[inv[t top + choice]][c] (times the choice's weight, if given)
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ inv, const float* __restrict__ weight_of,
+                                   float* __restrict__ y, int h, int top) {
     PDL_ENTER();
-    rows = pdl_fresh(rows); inv = pdl_fresh(inv); y = pdl_fresh(y);
+    rows = pdl_fresh(rows); inv = pdl_fresh(inv); y = pdl_fresh(y); weight_of = pdl_fresh(weight_of);
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < h; c += blockDim.x) {
         float a = y[(size_t)t * h + c];
-        for (int k = 0; k < top; ++k) a += rows[(size_t)inv[t * top + k] * h + c];
+        for (int k = 0; k < top; ++k) {
+            const float v = rows[(size_t)inv[t * top + k] * h + c];
+            a += weight_of != nullptr ? v * weight_of[t * top + k] : v;
+        }
         y[(size_t)t * h + c] = a;
     }
 }
 
-#define G_SMEM(NB) (G_STAGES * (GM + (NB) * GN) * GLD * 2)
+#define G_SMEM(MODE) (G_STAGES_OF(MODE) * (GM + ((MODE) == 0 ? 2 : 1) * GN) * GLD * 2)
 
 // Whether the tensor-core path takes these sizes: both inner sizes in whole steps of 64, rows 16-byte aligned.
 MB_API int mb_moe_fast_supported(int h, int ff) { return h % GK == 0 && ff % GK == 0 && h % 8 == 0 && ff % 8 == 0; }
 
-// xs bf16 [pairs][h], act bf16 [pairs][ff], rows float32 [pairs][h] (unused with top = 1), the int and float arrays [pairs].
-MB_API int mb_moe_experts_fast(const void* h_rows, const void* w_gate_up, const void* w_down, const int* expert_of, const float* weight_of,
-                               int* offsets, int* order, int* inv, int* token_sorted, float* weight_sorted, void* xs, void* act,
-                               float* rows, float* y, int tokens, int h, int ff, int E, int top, int weight_on_input, cudaStream_t s) {
-    if (tokens <= 0) return 0;
-    if (!mb_moe_fast_supported(h, ff) || E <= 0 || top <= 0 || (size_t)E * 8 > 48 * 1024) return MB_ERR_BAD_SIZE;
-    const int pairs = tokens * top;
-    int rc = launch_kernel(moe_group_kernel, 1, 1024, (size_t)E * 8, s, 0, expert_of, pairs, E, offsets, order);
-    if (rc != 0) return rc;
-    rc = launch_kernel(moe_gather_kernel<bf16>, pairs, 128, 0, s, 0, (const bf16*)h_rows, (const int*)order, weight_of, (bf16*)xs, token_sorted,
-                       weight_sorted, inv, h, top, weight_on_input);
-    if (rc != 0) return rc;
-    const int tiles = pairs / GM + E < pairs ? pairs / GM + E : pairs;          // at most one partial tile per expert
-    cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(2));
+static int grouped_tiles(int pairs, int E) { return pairs / GM + E < pairs ? pairs / GM + E : pairs; }   // at most one partial tile per expert
+
+// The pairs' inputs in expert order: xs bf16 [pairs][h], with each pair's token and weight beside it and where every pair went.
+MB_API int mb_moe_gather(const void* h_rows, const int* order, const float* weight_of, void* xs, int* token_sorted, float* weight_sorted,
+                         int* inv, int pairs, int h, int top, int weight_on_input, cudaStream_t s) {
+    if (pairs <= 0) return 0;
+    return launch_kernel(moe_gather_kernel<bf16>, pairs, 128, 0, s, 0, (const bf16*)h_rows, order, weight_of, (bf16*)xs, token_sorted,
+                         weight_sorted, inv, h, top, weight_on_input);
+}
+
+// act bf16 [pairs][ff] = silu(gate xs) * (up xs), expert by expert.
+MB_API int mb_moe_grouped_gate_up(const void* xs, const void* w_gate_up, const int* offsets, void* act, int pairs, int h, int ff, int E,
+                                  int interleaved, cudaStream_t s) {
+    if (pairs <= 0) return 0;
+    if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
+    cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(0));
+    return launch_kernel(moe_grouped_kernel<0>, dim3(grouped_tiles(pairs, E), (ff + GN - 1) / GN), 128, G_SMEM(0), s, 0, (const bf16*)xs,
+                         (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, (float*)nullptr, (const int*)nullptr, (const float*)nullptr, 0,
+                         interleaved);
+}
+
+// out float32 = down act, expert by expert: row i goes to row dst_rows[i] of out (null: row i), times row_scale[i] (null: 1),
+// added to what is there if `accumulate` (only where no two rows share a destination).
+MB_API int mb_moe_grouped_down(const void* act, const void* w_down, const int* offsets, float* out, const int* dst_rows,
+                               const float* row_scale, int accumulate, int pairs, int h, int ff, int E, cudaStream_t s) {
+    if (pairs <= 0) return 0;
+    if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
     cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(1));
-    rc = launch_kernel(moe_grouped_kernel<0>, dim3(tiles, (ff + GN - 1) / GN), 128, G_SMEM(2), s, 0, (const bf16*)xs, (const bf16*)w_gate_up,
-                       (const int*)offsets, E, ff, h, (bf16*)act, (float*)nullptr, (const int*)nullptr, (const float*)nullptr, 0);
-    if (rc != 0) return rc;
-    const float* scale = weight_on_input ? nullptr : weight_sorted;
-    if (top == 1)
-        return launch_kernel(moe_grouped_kernel<1>, dim3(tiles, (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act, (const bf16*)w_down,
-                             (const int*)offsets, E, h, ff, (bf16*)nullptr, y, (const int*)token_sorted, scale, 1);
-    rc = launch_kernel(moe_grouped_kernel<1>, dim3(tiles, (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act, (const bf16*)w_down,
-                       (const int*)offsets, E, h, ff, (bf16*)nullptr, rows, (const int*)nullptr, scale, 0);
-    if (rc != 0) return rc;
-    return launch_kernel(moe_combine_kernel, tokens, 256, 0, s, 0, (const float*)rows, (const int*)inv, y, h, top);
+    return launch_kernel(moe_grouped_kernel<1>, dim3(grouped_tiles(pairs, E), (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act,
+                         (const bf16*)w_down, offsets, E, h, ff, (bf16*)nullptr, out, dst_rows, row_scale, accumulate, 0);
+}
+
+MB_API int mb_moe_combine(const float* rows, const int* inv, const float* weight_of, float* y, int tokens, int h, int top, cudaStream_t s) {
+    if (tokens <= 0) return 0;
+    return launch_kernel(moe_combine_kernel, tokens, 256, 0, s, 0, rows, inv, weight_of, y, h, top);
 }

@@ -1231,11 +1231,14 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
             if launch_log is not None:
                 _cost(nd * per_row + 2 * _size(acc), 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
                 _pending_cost["rows"] = "decode"
-            _check(lib.mb_attn_sink_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(acc), _ptr(ml), _ptr(block_table),
+            _check(lib.mb_attn_sink_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(acc), _ptr(ml), _ptr(block_table),
                                            _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
-                                           _c_int(window), _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride),
-                                           _c_int(plan.split), _c_int(plan.chunks), _stream()), "attention (sink, decode)")
-            launches_extra(1)
+                                           _c_int(window), _c_int(chunk), _c_int(plan.split), _c_int(plan.chunks), _stream()),
+                   "attention (sink, decode)")
+            _cost(_size(acc) + nd * H * dv * size * (2 if gate is not None else 1))
+            _check(lib.mb_attn_sink_merge(_ptr(acc), _ptr(ml), _ptr(out), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(window),
+                                          _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _c_int(plan.split), _stream()),
+                   "attention (sink, parts merged)")
         if ctx.num_requests > nd:
             if launch_log is not None:
                 _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
@@ -1335,9 +1338,10 @@ def moe_group(experts: torch.Tensor, E: int, offsets: torch.Tensor, order: torch
 
 
 def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool) -> None:
+                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool, interleaved: bool = False) -> None:
     """``y[t] += sum_c down_e( silu(gate_e x) * (up_e x) )`` over token ``t``'s chosen experts ``e`` in choice order, ``x = w h[t]``
-    where the weight goes on the input, else the result times ``w``.  Any sizes, both dtypes."""
+    where the weight goes on the input, else the result times ``w``.  Any sizes, both dtypes.  ``interleaved``: an expert's
+    gate and up rows alternate in blocks of 16 (``interleave_gate_up``) instead of gate rows first."""
     _need_cuda(x, w_gate_up, w_down, experts, weights, act, y)
     T, h = x.shape
     top = experts.shape[1]
@@ -1345,11 +1349,15 @@ def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Te
     assert tuple(w_gate_up.shape[1:]) == (2 * ff, h) and tuple(w_down.shape[1:]) == (h, ff) and w_gate_up.dtype == x.dtype == w_down.dtype
     assert act.dtype == x.dtype and act.numel() >= T * top * ff and y.dtype == torch.float32 and tuple(y.shape) == (T, h)
     pairs = T * top
-    _cost(min(pairs, w_down.shape[0]) * 3 * ff * h * x.element_size() + _size(x) + 2 * _size(y), 6.0 * pairs * ff * h)
-    _check(_lib("mb_moe").mb_moe_experts_plain(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(act),
-                                              _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(top), _c_int(int(weight_on_input)),
-                                              _stream()), "experts")
-    launches_extra(1)
+    touched = min(pairs, w_down.shape[0])
+    for which, what in ((0, "experts, gate|up"), (1, "experts, down")):
+        if which == 0:
+            _cost(touched * 2 * ff * h * x.element_size() + _size(x) + pairs * ff * x.element_size(), 4.0 * pairs * ff * h)
+        else:
+            _cost(touched * ff * h * x.element_size() + pairs * ff * x.element_size() + 2 * _size(y), 2.0 * pairs * ff * h)
+        _check(_lib("mb_moe").mb_moe_experts_plain(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(act),
+                                                  _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(top), _c_int(int(weight_on_input)),
+                                                  _c_int(int(interleaved)), _c_int(which), _stream()), what)
 
 
 #: bf16 experts go to the grouped tensor-core kernels where the sizes allow (False: always the plain kernels)
@@ -1365,15 +1373,24 @@ def moe_jobs(dtype, h: int, ff: int) -> dict:
     return library_jobs("mb_moe")
 
 
+#: from this many (token, choice) pairs per expert on, a step that is not being captured in a graph reads the experts'
+#: counts back to the host and gives every expert's rows to the dense tcgen05 products (``gemm_swiglu``, ``gemm``) instead
+#: of the grouped mma.sync kernel
+EXPERTS_DENSE_FROM = 96
+
+
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                y: torch.Tensor, weight_on_input: bool, workspace) -> None:
-    """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``."""
+                y: torch.Tensor, weight_on_input: bool, workspace, interleaved: bool = False) -> None:
+    """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``.  bf16 with sizes in steps
+    of 64: the pairs are sorted by expert on the device and their inputs gathered in that order; then either two grouped
+    products over all experts (few pairs: single-token steps, captured or not: nothing is read back), or, with many pairs
+    per expert, the dense tensor-core products expert by expert over the sorted rows (the counts are read back once)."""
     T, top = experts.shape
     E, h, ff = w_down.shape
     pairs = T * top
     act = workspace.get("moe_act", (pairs, ff), x.dtype)
     if not (use_fast_experts and x.dtype == torch.bfloat16 and fast_experts_supported(h, ff)):
-        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input)
+        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input, interleaved)
         return
     _need_cuda(x, w_gate_up, w_down, experts, weights, y)
     assert tuple(w_gate_up.shape) == (E, 2 * ff, h) and w_gate_up.dtype == w_down.dtype == x.dtype and tuple(y.shape) == (T, h)
@@ -1382,12 +1399,37 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     offsets, order, inv, token_sorted = ints[:E + 1], ints[E + 1:E + 1 + pairs], ints[E + 1 + pairs:E + 1 + 2 * pairs], ints[E + 1 + 2 * pairs:]
     weight_sorted = workspace.get("moe_weight_sorted", (pairs,), torch.float32)
     xs = workspace.get("moe_xs", (pairs, h), x.dtype)
-    rows = workspace.get("moe_rows", (pairs, h), torch.float32) if top > 1 else None
     size = x.element_size()
-    _cost(min(pairs, E) * 3 * ff * h * size + 3 * pairs * h * size + 2 * pairs * ff * size + 2 * _size(y) + (2 * _size(rows) if rows is not None else 0),
-          6.0 * pairs * ff * h)
-    _check(_lib("mb_moe").mb_moe_experts_fast(
-        _ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(offsets), _ptr(order), _ptr(inv), _ptr(token_sorted),
-        _ptr(weight_sorted), _ptr(xs), _ptr(act), _ptr(rows), _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(E), _c_int(top),
-        _c_int(int(weight_on_input)), _stream()), "experts (grouped, tensor cores)")
-    launches_extra(3 if top == 1 else 4)
+    lib = _lib("mb_moe")
+    touched = min(pairs, E)
+    moe_group(experts, E, offsets, order)
+    _cost(2 * pairs * h * size)
+    _check(lib.mb_moe_gather(_ptr(x), _ptr(order), _ptr(weights), _ptr(xs), _ptr(token_sorted), _ptr(weight_sorted), _ptr(inv), _c_int(pairs),
+                             _c_int(h), _c_int(top), _c_int(int(weight_on_input)), _stream()), "experts' inputs gathered")
+    dense = (interleaved and pairs >= EXPERTS_DENSE_FROM * E and use_tensor_cores and not torch.cuda.is_current_stream_capturing())
+    if dense:
+        rows = workspace.get("moe_rows", (pairs, h), torch.float32)
+        bounds = offsets.tolist()                       # the one wait on the host: how many pairs each expert got
+        for e in range(E):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
+                gemm(act[lo:hi], w_down[e], rows[lo:hi])
+        _cost(_size(rows) + 2 * _size(y))
+        _check(lib.mb_moe_combine(_ptr(rows), _ptr(inv), _ptr(None if weight_on_input else weights), _ptr(y), _c_int(T), _c_int(h),
+                                  _c_int(top), _stream()), "experts' outputs added")
+        return
+    _cost(touched * 2 * ff * h * size + pairs * (h + ff) * size, 4.0 * pairs * ff * h)
+    _check(lib.mb_moe_grouped_gate_up(_ptr(xs), _ptr(w_gate_up), _ptr(offsets), _ptr(act), _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E),
+                                      _c_int(int(interleaved)), _stream()), "experts, gate|up, SwiGLU (grouped, tensor cores)")
+    scale = None if weight_on_input else weight_sorted
+    _cost(touched * ff * h * size + pairs * ff * size + 2 * pairs * h * 4, 2.0 * pairs * ff * h)
+    if top == 1:           # every pair has a row of y to itself: the product adds into it
+        _check(lib.mb_moe_grouped_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), _ptr(token_sorted), _ptr(scale), _c_int(1),
+                                       _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E), _stream()), "experts, down (grouped, tensor cores)")
+        return
+    rows = workspace.get("moe_rows", (pairs, h), torch.float32)
+    _check(lib.mb_moe_grouped_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(rows), _ptr(None), _ptr(scale), _c_int(0),
+                                   _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E), _stream()), "experts, down (grouped, tensor cores)")
+    _cost(_size(rows) + 2 * _size(y))
+    _check(lib.mb_moe_combine(_ptr(rows), _ptr(inv), _ptr(None), _ptr(y), _c_int(T), _c_int(h), _c_int(top), _stream()), "experts' outputs added")

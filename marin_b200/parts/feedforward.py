@@ -146,8 +146,12 @@ class RoutedExperts(FeedForward):
         return specs + [TensorSpec(self._n("router"), (self.experts, h), "bias")]
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
-        # one tensor per kind for all experts: gate rows then up rows of an expert side by side, [E, 2 ff, h]; down [E, h, ff]
-        self.w_gate_up = rt.matrix(torch.stack([torch.cat([tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e))], dim=0)
+        # one tensor per kind for all experts: an expert's gate and up rows in one matrix, [E, 2 ff, h]; down [E, h, ff].  Where
+        # the dense product's SwiGLU epilogue applies, the rows alternate in blocks of 16 as it reads them, so that an expert
+        # with many tokens can go to that product as it is; otherwise gate rows come first.
+        self.interleaved = ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
+        join = ops.interleave_gate_up if self.interleaved else (lambda g, u: torch.cat([g, u], dim=0))
+        self.w_gate_up = rt.matrix(torch.stack([join(tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e)))
                                                 for e in range(self.experts)]))
         self.w_down = rt.matrix(torch.stack([tensors.pop(self._n("down", e)) for e in range(self.experts)]))
         self.router = rt.f32(tensors.pop(self._n("router")))
@@ -172,5 +176,5 @@ class RoutedExperts(FeedForward):
         ops.stage_name = "router"
         ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize)
         ops.stage_name = "experts"
-        ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws)
+        ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws, self.interleaved)
         return None

@@ -31,7 +31,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
 LENGTHS = {"A": {"a": 37, "b": 9, "c": 150, "d": 1, "e": 66, "f": 41, "g": 27},
            "B": {"a": 100, "b": 1, "c": 190, "d": 17, "e": 64},
-           "C": {"a": 140, "b": 2, "c": 65, "d": 300, "e": 31, "f": 129},
+           "C": {"a": 140, "b": 2, "c": 65, "d": 300, "e": 31, "f": 129, "g": 400},
            "D": {"a": 33, "b": 3, "c": 80, "d": 1, "e": 19}}
 
 
