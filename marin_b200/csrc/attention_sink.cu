@@ -15,7 +15,7 @@
 #include "common.cuh"
 #include "launch.cuh"
 
-#define QF_THREADS 256
+#define QF_THREADS 256            // at least; 1024 where a token's q and k have 4,096 elements and more
 
 // ---- heads of the fused q|k|v(|g) projection, a token per block ---------------------------------------------------------
 // A row of `row` holds q (H heads of d), k (K heads of d), v (K heads of dv), then whatever follows (the gate's columns).
@@ -25,7 +25,7 @@
 // v_mode 0: values as they are; 1: they are also left in v_shared (activation dtype [tokens][K dv]) for later layers;
 // 2: v <- (1 - lam) v + lam v_shared, lam = *v_lambda, and the mixed values go to the cache.
 template <typename T>
-__global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
+__global__ void __launch_bounds__(1024) qkv_finish_kernel(
     const T* __restrict__ row, int row_stride, T* __restrict__ q_out, const float* __restrict__ q_b, const float* __restrict__ k_b,
     const float* __restrict__ v_b, int norm_mode, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim, float rot_mag,
@@ -41,11 +41,11 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
     float* head_ss = cs_tab + 2 * half;        // [heads]
     __shared__ float s_factor[2];
     const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = QF_THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x / 32, threads = blockDim.x;
     const T* src = row + (size_t)t * row_stride;
     if (inv_freq != nullptr) {
         const float pos = (float)positions[t];
-        for (int i = threadIdx.x; i < half; i += QF_THREADS) {
+        for (int i = threadIdx.x; i < half; i += threads) {
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
             cs_tab[i] = cs * rot_mag;
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
     }
     // every element of q and k (+ bias) into shared memory as float32, all threads side by side
     const int qk = heads * d, q_len = H * d;
-    for (int idx = threadIdx.x; idx < qk; idx += QF_THREADS) {
+    for (int idx = threadIdx.x; idx < qk; idx += threads) {
         float v = to_f32(src[idx]);
         if (idx < q_len) { if (q_b != nullptr) v += q_b[idx]; }
         else if (k_b != nullptr) v += k_b[idx - q_len];
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
     __syncthreads();
     const int slot = write_kv ? slot_mapping[t] : -1;
     T* k_dst = slot >= 0 ? k_cache + (((size_t)(slot / page_size)) * K * page_size + (size_t)(slot % page_size)) * d : nullptr;
-    for (int idx = threadIdx.x; idx < qk; idx += QF_THREADS) {
+    for (int idx = threadIdx.x; idx < qk; idx += threads) {
         const int head = idx / d, i = idx - head * d;
         const bool is_q = head < H;
         const int kh = head - H;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(QF_THREADS) qkv_finish_kernel(
     if (!write_kv) return;
     const float lam = v_mode == 2 ? *v_lambda : 0.0f;
     const int vcol0 = (H + K) * d;
-    for (int i = threadIdx.x; i < K * dv; i += QF_THREADS) {
+    for (int i = threadIdx.x; i < K * dv; i += threads) {
         float v = to_f32(src[vcol0 + i]);
         if (v_b != nullptr) v += v_b[i];
         if (v_mode == 1) v_shared[(size_t)t * K * dv + i] = from_f32<T>(v);
@@ -135,7 +135,7 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
             const int rc = (int)cudaFuncSetAttribute(qkv_finish_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (rc != 0) return rc;                                                                                                  \
         }                                                                                                                            \
-        return launch_kernel(qkv_finish_kernel<TT>, tokens, QF_THREADS, smem, s, 0, (const TT*)row, row_stride, (TT*)q_out, q_b, k_b, \
+        return launch_kernel(qkv_finish_kernel<TT>, tokens, (H + K) * d >= 4096 ? 1024 : QF_THREADS, smem, s, 0, (const TT*)row, row_stride, (TT*)q_out, q_b, k_b, \
                              v_b, norm_mode, q_w, k_w, eps, positions, inv_freq, rot_dim, rot_mag, slot_mapping, (TT*)k_cache,      \
                              (TT*)v_cache, v_mode, (TT*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv);                       \
     } while (0)

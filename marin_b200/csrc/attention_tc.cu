@@ -186,11 +186,19 @@ MB_API int mb_attn_prefill_tc_probe_read(long long* host) { return (int)cudaMemc
 #define TA_OUT(slot, v) do { (void)(v); } while (0)
 #endif
 
+// The first key position `pos` sees: the last `window` positions (0: all), and of those only its own chunk of `chunk`
+// positions, counted from the sequence's first (0: no chunks).
+__device__ __forceinline__ int first_seen(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+    return lo;
+}
+
 __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
-    int box_rows) {
+    int box_rows, int chunk, int sink, const bf16* __restrict__ gate, int gate_stride) {
     extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
@@ -229,7 +237,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     const int q_first = pos0 + qt * TA_BM, q_last = q_first + rows - 1;
-    const int k_lo = window > 0 ? max(0, q_first - window + 1) : 0;
+    const int k_lo = first_seen(q_first, window, chunk);   // the first key a position sees never decreases with the position
     const int kh = h / GROUP;
     const int kb_first = k_lo / TA_BN, kb_last = q_last / TA_BN;
     const int nblk = kb_last - kb_first + 1;
@@ -382,10 +390,12 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
         // ---- the rows: thread t owns query row t ----
         const int row_t = threadIdx.x;
         const int qp = q_first + row_t;
-        const int lo_t = window > 0 ? max(0, qp - window + 1) : 0;
+        const int lo_t = first_seen(qp, window, chunk);
         const float sl2 = scale * 1.4426950408889634f;
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float m_used = -INFINITY, l_run = 0.0f;           // the maximum O and l are currently scaled by (log2 units)
+        // the maximum O and l are currently scaled by (log2 units); a sink is a key of score 0 without a value: the maximum
+        // starts at 0 and the sum at 1
+        float m_used = sink ? 0.0f : -INFINITY, l_run = sink ? 1.0f : 0.0f;
         bool ok = true;
         long long r_s = 0, r_o = 0;
         const long long r_start = TA_T();
@@ -400,7 +410,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // two passes over the 64 scores, 32 at a time (tensor memory is cheap to read twice; registers are not):
             // the row maximum first, then the probabilities
-            const bool interior = key0 + TA_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
+            const bool interior = key0 + TA_BN - 1 <= q_first && key0 >= first_seen(q_last, window, chunk);
             float mx = -INFINITY;
             {
                 float s[64];
@@ -479,10 +489,24 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l_run;
             bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
+            const bf16* grow = (gate != nullptr && row_t < rows) ? gate + (size_t)(tok0 + qt * TA_BM + row_t) * gate_stride + (size_t)h * D : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 float ov[32];
                 tmem_ld32(lane_base + TA_O_COL + c * 32, ov);
+                if (grow != nullptr) {                         // an output gate: times sigmoid(g), element by element
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        const uint4 graw = *reinterpret_cast<const uint4*>(grow + c * 32 + q8 * 8);
+                        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 gg = __bfloat1622float2(g2[e]);
+                            ov[q8 * 8 + 2 * e] *= __fdividef(1.0f, 1.0f + ta_exp2(gg.x * -1.4426950408889634f));
+                            ov[q8 * 8 + 2 * e + 1] *= __fdividef(1.0f, 1.0f + ta_exp2(gg.y * -1.4426950408889634f));
+                        }
+                    }
+                }
                 if (row_t < rows) {
 #pragma unroll
                     for (int q8 = 0; q8 < 4; ++q8) {
@@ -523,8 +547,9 @@ static int map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                               int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int requests,
                               int max_query_len, int tokens, int K, int page_size, long long cache_pages, float scale,
-                              int window, int* error_flag, cudaStream_t s) {
+                              int window, int* error_flag, int chunk, int sink, const void* gate, int gate_stride, cudaStream_t s) {
     if (requests <= 0 || max_query_len <= 0) return 0;
+    if (chunk < 0 || (gate != nullptr && (((uintptr_t)gate & 15) || gate_stride % 8 != 0))) return MB_ERR_BAD_SIZE;
     int page_shift = -1;
     for (int b = 4; b < 16; ++b)
         if ((1 << b) == page_size) page_shift = b;
@@ -547,5 +572,5 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
     return launch_kernel(attn_prefill_tc_kernel, grid, 256, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
-                         seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows);
+                         seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows, chunk, sink, (const bf16*)gate, gate_stride);
 }

@@ -32,8 +32,8 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restri
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows);
     extern __shared__ float smem[];
-    float* z = smem;                           // [E]
-    float* xrow = smem + E;                    // [h]
+    float* xrow = smem;                        // [h] (first: 16-byte aligned)
+    float* z = smem + h;                       // [E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const T* x = h_rows + (size_t)t * h;
@@ -43,6 +43,25 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restri
         const float* w = router + (size_t)e * h;
         float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
         int i = lane;
+        if ((h & 3) == 0 && (((uintptr_t)w) & 15) == 0) {         // 16-byte loads, four of them in flight
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* x4 = reinterpret_cast<const float4*>(xrow);
+            const int n4 = h >> 2;
+            int j = lane;
+            for (; j + 96 < n4; j += 128) {
+                const float4 a0 = w4[j], a1 = w4[j + 32], a2 = w4[j + 64], a3 = w4[j + 96];
+                const float4 b0 = x4[j], b1 = x4[j + 32], b2 = x4[j + 64], b3 = x4[j + 96];
+                d0 = fmaf(b0.x, a0.x, fmaf(b0.y, a0.y, fmaf(b0.z, a0.z, fmaf(b0.w, a0.w, d0))));
+                d1 = fmaf(b1.x, a1.x, fmaf(b1.y, a1.y, fmaf(b1.z, a1.z, fmaf(b1.w, a1.w, d1))));
+                d2 = fmaf(b2.x, a2.x, fmaf(b2.y, a2.y, fmaf(b2.z, a2.z, fmaf(b2.w, a2.w, d2))));
+                d3 = fmaf(b3.x, a3.x, fmaf(b3.y, a3.y, fmaf(b3.z, a3.z, fmaf(b3.w, a3.w, d3))));
+            }
+            for (; j < n4; j += 32) {
+                const float4 a0 = w4[j], b0 = x4[j];
+                d0 = fmaf(b0.x, a0.x, fmaf(b0.y, a0.y, fmaf(b0.z, a0.z, fmaf(b0.w, a0.w, d0))));
+            }
+            i = h;
+        }
         for (; i + 96 < h; i += 128) {
             d0 = fmaf(xrow[i], w[i], d0); d1 = fmaf(xrow[i + 32], w[i + 32], d1);
             d2 = fmaf(xrow[i + 64], w[i + 64], d2); d3 = fmaf(xrow[i + 96], w[i + 96], d3);

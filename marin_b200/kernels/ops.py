@@ -688,7 +688,8 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
                                          _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                          _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
-                                         _ptr(_scratch_for(q.device).error), _stream()), "attention (prefill, tensor cores)")
+                                         _ptr(_scratch_for(q.device).error), _c_int(0), _c_int(0), _ptr(None), _c_int(0), _stream()),
+                   "attention (prefill, tensor cores)")
         elif ctx.num_requests > nd:
             _attention_cost(q, T - nd, H, K, d, "prefill")
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
@@ -1239,10 +1240,21 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
             _check(lib.mb_attn_sink_merge(_ptr(acc), _ptr(ml), _ptr(out), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(window),
                                           _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _c_int(plan.split), _stream()),
                    "attention (sink, parts merged)")
-        if ctx.num_requests > nd:
-            if launch_log is not None:
-                _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
-                _pending_cost["rows"] = "prefill"
+        if ctx.num_requests > nd and launch_log is not None:
+            _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+            _pending_cost["rows"] = "prefill"
+        if (ctx.num_requests > nd and use_tc_attention and d == dv and d in (64, 128) and page_size >= 16
+                and (gate is None or (gate.data_ptr() % 16 == 0 and gate_stride % 8 == 0))):
+            # heads of 64 or 128 with values as wide: the tcgen05 kernel that plain causal attention uses takes the chunked
+            # mask, the sink and the gate as parameters
+            tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
+            _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                         _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                                         _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
+                                         ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
+                                         _ptr(_scratch_for(q.device).error), _c_int(chunk), _c_int(int(sink)), _ptr(gate),
+                                         _c_int(gate_stride), _stream()), "attention (sink, prefill, tensor cores)")
+        elif ctx.num_requests > nd:
             _check(lib.mb_attn_sink_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                             _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                             _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_int(window),
@@ -1281,6 +1293,8 @@ def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
     jobs = library_jobs("mb_attention_sink")
     if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv):
         jobs[f"mb_attention_sink_fast_d{d}_v{dv}_g{H // K}"] = _sink_job(d, dv, H // K)
+        if d == dv and d in (64, 128):
+            jobs[f"mb_attention_tc_d{d}_g{H // K}"] = build.attention_tc_job(d, H // K)
     return jobs
 
 

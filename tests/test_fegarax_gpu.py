@@ -202,6 +202,7 @@ YARN = {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}
     {"heads": 3, "kv_heads": 3, "dim": 32, "vdim": 16, "scale": 0.2, "mask": {"size": 1}, "rot": {"base": 100.0, "dims": 32}},
     {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 16}, "rot": {"base": 500.0, "dims": 32, "scaling": YARN}},
     {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09, "mask": {"size": 50}},
+    {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.09, "mask": {"size": 50}, "rot": {"base": 500.0, "dims": 64, "scaling": YARN}},
     {"heads": 2, "kv_heads": 1, "dim": 80, "vdim": 48, "scale": 0.11, "rot": {"base": 100.0, "dims": 80, "scaling": YARN}},
     {"heads": 8, "kv_heads": 1, "dim": 16, "vdim": 128, "scale": 0.25, "mask": {"size": 64}, "rot": {"base": 100.0, "dims": 2}},
     {"heads": 6, "kv_heads": 2, "dim": 8, "vdim": 520, "scale": 0.35, "mask": {"size": 7}},
@@ -222,8 +223,15 @@ def test_attention_alone(dtype, m):
     mixer.load(dict(w), rt)
     x = torch.randn(61, hidden, generator=torch.Generator().manual_seed(2)).to(rt.dtype)
     want = plain_mixer(x, w, m)
+    # heads of 64 or 128 with values as wide and pages of 16: prompt portions go to the kernel plain causal attention uses
+    page = 16 if m["dim"] == m["vdim"] and m["dim"] in (64, 128) else 8
     for cuts in CUTS:
-        close(feed([mixer], harness([mixer.cache_need()], rt), x, cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+        close(feed([mixer], harness([mixer.cache_need()], rt, page=page), x, cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+    if page == 16:        # and a longer sequence: several key blocks, chunk edges inside and on block borders
+        x = torch.randn(333, hidden, generator=torch.Generator().manual_seed(3)).to(rt.dtype)
+        want = plain_mixer(x, w, m)
+        for cuts in ([333], [130, 1, 1, 201], [64, 64, 64, 141]):
+            close(feed([mixer], harness([mixer.cache_need()], rt, page=page), x, cuts)[0], want, dtype, f"long, cuts {cuts[:4]}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
