@@ -135,7 +135,7 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
             const int rc = (int)cudaFuncSetAttribute(qkv_finish_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (rc != 0) return rc;                                                                                                  \
         }                                                                                                                            \
-        return launch_kernel(qkv_finish_kernel<TT>, tokens, (H + K) * d >= 4096 ? 1024 : QF_THREADS, smem, s, 0, (const TT*)row, row_stride, (TT*)q_out, q_b, k_b, \
+        return launch_kernel(qkv_finish_kernel<TT>, tokens, (H + K) * d < 4096 ? QF_THREADS : tokens <= 64 ? 1024 : 512, smem, s, 0, (const TT*)row, row_stride, (TT*)q_out, q_b, k_b, \
                              v_b, norm_mode, q_w, k_w, eps, positions, inv_freq, rot_dim, rot_mag, slot_mapping, (TT*)k_cache,      \
                              (TT*)v_cache, v_mode, (TT*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv);                       \
     } while (0)

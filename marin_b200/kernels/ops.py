@@ -1391,6 +1391,17 @@ def moe_jobs(dtype, h: int, ff: int) -> dict:
 #: counts back to the host and gives every expert's rows to the dense tcgen05 products (``gemm_swiglu``, ``gemm``) instead
 #: of the grouped mma.sync kernel
 EXPERTS_DENSE_FROM = 96
+#: streams the experts' dense products are dealt over: one expert's products fill the device only partly (a quarter of the
+#: step's rows, tiles that do not make whole rounds over the SMs), several at a time fill the gaps.  1: one after the other.
+EXPERT_STREAMS = 4
+_side_streams = {}
+
+
+def _expert_streams(device, n: int):
+    key = (device.index, n)
+    if key not in _side_streams:
+        _side_streams[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+    return _side_streams[key]
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
@@ -1424,11 +1435,35 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     if dense:
         rows = workspace.get("moe_rows", (pairs, h), torch.float32)
         bounds = offsets.tolist()                       # the one wait on the host: how many pairs each expert got
-        for e in range(E):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
+        active = [e for e in range(E) if bounds[e + 1] > bounds[e]]
+        # (while the stages of a step are being recorded everything stays on one stream, in launch order)
+        lanes = min(EXPERT_STREAMS, len(active)) if launch_log is None else 1
+        if lanes <= 1:
+            for e in active:
+                lo, hi = bounds[e], bounds[e + 1]
                 gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
                 gemm(act[lo:hi], w_down[e], rows[lo:hi])
+        else:
+            global stream_k
+            current = torch.cuda.current_stream(x.device)
+            side = _expert_streams(x.device, lanes)
+            ready = torch.cuda.Event()
+            ready.record(current)
+            keep, stream_k = stream_k, False            # stream-K parks tiles in scratch memory that one stream of work owns
+            try:
+                for i, e in enumerate(active):
+                    lo, hi = bounds[e], bounds[e + 1]
+                    if i < lanes:
+                        side[i].wait_event(ready)
+                    with torch.cuda.stream(side[i % lanes]):
+                        gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
+                        gemm(act[lo:hi], w_down[e], rows[lo:hi])
+            finally:
+                stream_k = keep
+            for st in side:
+                done = torch.cuda.Event()
+                done.record(st)
+                current.wait_event(done)
         _cost(_size(rows) + 2 * _size(y))
         _check(lib.mb_moe_combine(_ptr(rows), _ptr(inv), _ptr(None if weight_on_input else weights), _ptr(y), _c_int(T), _c_int(h),
                                   _c_int(top), _stream()), "experts' outputs added")
