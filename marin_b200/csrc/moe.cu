@@ -245,7 +245,6 @@ MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gat
 // A pair's row is computed from that row's operands alone, whichever tile it lands in.
 #include "mma_helpers.cuh"
 
-#define GM 64
 #define GN 64
 #define GK 64
 #define GLD (GK + 8)
@@ -270,7 +269,10 @@ __global__ void moe_gather_kernel(const T* __restrict__ h_rows, const int* __res
 
 // MODE 0: W [E][2 N][K] (gate rows, then up rows), result silu(gate) * up as bf16 [rows][N].
 // MODE 1: W [E][N][K], result float32: row r goes to dst_rows[r] (null: r), times row_scale[r] (null: 1), added if `accumulate`.
-template <int MODE>
+// GMT: pairs per tile, 16, 32 or 64.  The four warps take 16 rows each where the tile has 64, two row groups x two column
+// groups where it has 32, four column groups of 16 where it has 16: with few pairs per expert (single-token steps) a tile of
+// 64 rows would spend the tensor pipe on rows that hold nothing (measured: 45 % of its cycles on 2 live rows of 64).
+template <int MODE, int GMT>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
                                                           const int* __restrict__ offsets, int E, int N, int K, bf16* __restrict__ act_out,
                                                           float* __restrict__ f_out, const int* __restrict__ dst_rows,
@@ -279,25 +281,27 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
     A = pdl_fresh(A); offsets = pdl_fresh(offsets); dst_rows = pdl_fresh(dst_rows); row_scale = pdl_fresh(row_scale); f_out = pdl_fresh(f_out);
     constexpr int NB = MODE == 0 ? 2 : 1;
     constexpr int G_STAGES = G_STAGES_OF(MODE);
+    constexpr int WR = GMT / 16, WC = 4 / WR, NT = (GN / 8) / WC;       // row groups, column groups, 8-column tiles per warp
     extern __shared__ __align__(16) uint8_t g_smem[];
-    bf16* sA = reinterpret_cast<bf16*>(g_smem);                              // [G_STAGES][GM][GLD]
-    bf16* sB = sA + G_STAGES * GM * GLD;                                     // [G_STAGES][NB][GN][GLD]
+    bf16* sA = reinterpret_cast<bf16*>(g_smem);                              // [G_STAGES][GMT][GLD]
+    bf16* sB = sA + G_STAGES * GMT * GLD;                                    // [G_STAGES][NB][GN][GLD]
     // which expert's which tile this CTA is: tiles are numbered expert after expert
     int tile = blockIdx.x, e = 0, row0 = -1, row_end = 0;
     for (e = 0; e < E; ++e) {
         const int b = offsets[e], n = offsets[e + 1] - b;
-        const int tiles = (n + GM - 1) / GM;
-        if (tile < tiles) { row0 = b + tile * GM; row_end = b + n; break; }
+        const int tiles = (n + GMT - 1) / GMT;
+        if (tile < tiles) { row0 = b + tile * GMT; row_end = b + n; break; }
         tile -= tiles;
     }
     if (row0 < 0) return;
     const int col0 = blockIdx.y * GN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bf16* We = W + (size_t)e * NB * N * K;
-    const int a_rows = min(GM, row_end - row0), b_rows = min(GN, N - col0);
+    const int a_rows = min(GMT, row_end - row0), b_rows = min(GN, N - col0);
+    const int warp_r = warp % WR, warp_c = warp / WR;
     // rows of a tile past the expert's pairs, or past the last column, are zero in every stage and are never copied into
-    for (int idx = threadIdx.x; idx < G_STAGES * GM * (GK / 8); idx += 128) {
-        const int r = (idx / (GK / 8)) % GM;
+    for (int idx = threadIdx.x; idx < G_STAGES * GMT * (GK / 8); idx += 128) {
+        const int r = (idx / (GK / 8)) % GMT;
         if (r >= a_rows) *reinterpret_cast<uint4*>(sA + (idx / (GK / 8)) * GLD + (idx % (GK / 8)) * 8) = make_uint4(0, 0, 0, 0);
     }
     if (b_rows < GN)
@@ -307,7 +311,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
         }
     auto load = [&](int stage, int kt) {
         const int k0 = kt * GK;
-        bf16* a = sA + stage * GM * GLD;
+        bf16* a = sA + stage * GMT * GLD;
         for (int idx = threadIdx.x; idx < a_rows * (GK / 8); idx += 128) {
             const int r = idx / (GK / 8), c = idx % (GK / 8);
             cp_async16(a + r * GLD + c * 8, A + (size_t)(row0 + r) * K + k0 + c * 8);
@@ -322,11 +326,11 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
             }
         }
     };
-    float acc[NB][GN / 8][4];
+    float acc[NB][NT][4];
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int j = 0; j < GN / 8; ++j) { acc[nb][j][0] = acc[nb][j][1] = acc[nb][j][2] = acc[nb][j][3] = 0.0f; }
+        for (int j = 0; j < NT; ++j) { acc[nb][j][0] = acc[nb][j][1] = acc[nb][j][2] = acc[nb][j][3] = 0.0f; }
     const int nk = K / GK;
 #pragma unroll
     for (int s = 0; s < G_STAGES - 1; ++s) {
@@ -339,16 +343,16 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
         if (kt + G_STAGES - 1 < nk) load((kt + G_STAGES - 1) % G_STAGES, kt + G_STAGES - 1);
         cp_async_commit();
         const int stage = kt % G_STAGES;
-        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sA + stage * GM * GLD + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * GLD + (lane >> 4) * 8);
+        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sA + stage * GMT * GLD + (warp_r * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * GLD + (lane >> 4) * 8);
 #pragma unroll
         for (int kk = 0; kk < GK / 16; ++kk) {
             uint32_t a[4];
             ldsm_x4(a_addr + kk * 32, a[0], a[1], a[2], a[3]);
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
-                const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(sB + (stage * NB + nb) * GN * GLD + ((lane & 7) + (lane >> 4) * 8) * GLD + ((lane >> 3) & 1) * 8);
+                const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(sB + (stage * NB + nb) * GN * GLD + (warp_c * NT * 8 + (lane & 7) + (lane >> 4) * 8) * GLD + ((lane >> 3) & 1) * 8);
 #pragma unroll
-                for (int j = 0; j < GN / 8; j += 2) {
+                for (int j = 0; j < NT; j += 2) {
                     uint32_t b0, b1, b2, b3;
                     ldsm_x4(b_addr + (uint32_t)(j * 8 * GLD * 2 + kk * 32), b0, b1, b2, b3);
                     mma_bf16_16816(acc[nb][j], a, b0, b1);
@@ -358,15 +362,15 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
         }
     }
     cp_async_wait<0>();
-    const int col = col0 + 2 * (lane & 3);
+    const int col = col0 + warp_c * NT * 8 + 2 * (lane & 3);
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
-        const int row = row0 + warp * 16 + (lane >> 2) + 8 * rr;
+        const int row = row0 + warp_r * 16 + (lane >> 2) + 8 * rr;
         if (row >= row_end) continue;
         if (MODE == 0) {
             bf16* dst = act_out + (size_t)row * N;
 #pragma unroll
-            for (int j = 0; j < GN / 8; ++j) {
+            for (int j = 0; j < NT; ++j) {
                 const int c = col + j * 8;
                 if (c < N) {                                   // N is even: a pair of columns is inside or outside together
                     const float g0 = acc[0][j][2 * rr], g1 = acc[0][j][2 * rr + 1];
@@ -379,7 +383,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
             const float f = row_scale != nullptr ? row_scale[row] : 1.0f;
             float* dst = f_out + to * N;
 #pragma unroll
-            for (int j = 0; j < GN / 8; ++j) {
+            for (int j = 0; j < NT; ++j) {
                 const int c = col + j * 8;
                 if (c < N) {
                     float2 v = make_float2(acc[0][j][2 * rr] * f, acc[0][j][2 * rr + 1] * f);
@@ -407,12 +411,33 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
     }
 }
 
-#define G_SMEM(MODE) (G_STAGES_OF(MODE) * (GM + ((MODE) == 0 ? 2 : 1) * GN) * GLD * 2)
+#define G_SMEM(MODE, GMT) (G_STAGES_OF(MODE) * ((GMT) + ((MODE) == 0 ? 2 : 1) * GN) * GLD * 2)
 
 // Whether the tensor-core path takes these sizes: both inner sizes in whole steps of 64, rows 16-byte aligned.
 MB_API int mb_moe_fast_supported(int h, int ff) { return h % GK == 0 && ff % GK == 0 && h % 8 == 0 && ff % 8 == 0; }
 
-static int grouped_tiles(int pairs, int E) { return pairs / GM + E < pairs ? pairs / GM + E : pairs; }   // at most one partial tile per expert
+static int grouped_tiles(int pairs, int E, int gm) { return pairs / gm + E < pairs ? pairs / gm + E : pairs; }   // at most one partial tile per expert
+
+// Pairs per tile: as few rows as the experts' shares need (the shares are not known on the host: their average decides).
+static int grouped_rows(int pairs, int E) { return pairs <= 8 * E ? 16 : pairs <= 24 * E ? 32 : 64; }
+
+template <int MODE, int GMT>
+static int grouped_launch(const bf16* A, const bf16* W, const int* offsets, int E, int N, int K, bf16* act, float* out, const int* dst_rows,
+                          const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s) {
+    cudaFuncSetAttribute(moe_grouped_kernel<MODE, GMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(MODE, GMT));
+    return launch_kernel(moe_grouped_kernel<MODE, GMT>, dim3(grouped_tiles(pairs, E, GMT), (N + GN - 1) / GN), 128, G_SMEM(MODE, GMT), s, 0, A, W,
+                         offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved);
+}
+
+template <int MODE>
+static int grouped_by_rows(const bf16* A, const bf16* W, const int* offsets, int E, int N, int K, bf16* act, float* out, const int* dst_rows,
+                           const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s) {
+    switch (grouped_rows(pairs, E)) {
+        case 16: return grouped_launch<MODE, 16>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
+        case 32: return grouped_launch<MODE, 32>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
+    }
+    return grouped_launch<MODE, 64>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
+}
 
 // The pairs' inputs in expert order: xs bf16 [pairs][h], with each pair's token and weight beside it and where every pair went.
 MB_API int mb_moe_gather(const void* h_rows, const int* order, const float* weight_of, void* xs, int* token_sorted, float* weight_sorted,
@@ -427,10 +452,8 @@ MB_API int mb_moe_grouped_gate_up(const void* xs, const void* w_gate_up, const i
                                   int interleaved, cudaStream_t s) {
     if (pairs <= 0) return 0;
     if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
-    cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(0));
-    return launch_kernel(moe_grouped_kernel<0>, dim3(grouped_tiles(pairs, E), (ff + GN - 1) / GN), 128, G_SMEM(0), s, 0, (const bf16*)xs,
-                         (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, (float*)nullptr, (const int*)nullptr, (const float*)nullptr, 0,
-                         interleaved);
+    return grouped_by_rows<0>((const bf16*)xs, (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, nullptr, nullptr, nullptr, 0, interleaved,
+                              pairs, s);
 }
 
 // out float32 = down act, expert by expert: row i goes to row dst_rows[i] of out (null: row i), times row_scale[i] (null: 1),
@@ -439,9 +462,7 @@ MB_API int mb_moe_grouped_down(const void* act, const void* w_down, const int* o
                                const float* row_scale, int accumulate, int pairs, int h, int ff, int E, cudaStream_t s) {
     if (pairs <= 0) return 0;
     if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
-    cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(1));
-    return launch_kernel(moe_grouped_kernel<1>, dim3(grouped_tiles(pairs, E), (h + GN - 1) / GN), 128, G_SMEM(1), s, 0, (const bf16*)act,
-                         (const bf16*)w_down, offsets, E, h, ff, (bf16*)nullptr, out, dst_rows, row_scale, accumulate, 0);
+    return grouped_by_rows<1>((const bf16*)act, (const bf16*)w_down, offsets, E, h, ff, nullptr, out, dst_rows, row_scale, accumulate, 0, pairs, s);
 }
 
 MB_API int mb_moe_combine(const float* rows, const int* inv, const float* weight_of, float* y, int tokens, int h, int top, cudaStream_t s) {
