@@ -78,8 +78,8 @@ __global__ void __launch_bounds__(1024) qkv_finish_kernel(
     __syncthreads();
     const int slot = write_kv ? slot_mapping[t] : -1;
     T* k_dst = slot >= 0 ? k_cache + (((size_t)(slot / page_size)) * K * page_size + (size_t)(slot % page_size)) * d : nullptr;
-    for (int idx = threadIdx.x; idx < qk; idx += threads) {
-        const int head = idx / d, i = idx - head * d;
+    // a warp per head, lanes along the head: no division per element, 64-byte runs per store
+    for (int head = warp; head < heads; head += warps) {
         const bool is_q = head < H;
         const int kh = head - H;
         if (!is_q && k_dst == nullptr) continue;
@@ -92,31 +92,209 @@ __global__ void __launch_bounds__(1024) qkv_finish_kernel(
             factor = s_factor[is_q ? 0 : 1];
             w = is_q ? q_w + (size_t)head * d : k_w + (size_t)kh * d;
         }
-        float a = vals[idx] * factor * (w != nullptr ? w[i] : 1.0f);
-        if (inv_freq != nullptr && i < rot_dim) {
-            const bool low = i < half;
-            const int j = low ? i : i - half, other = low ? i + half : i - half;
-            const float b = vals[head * d + other] * factor * (w != nullptr ? w[other] : 1.0f);
-            const float cs = cs_tab[j], sn = cs_tab[half + j];
-            a = low ? a * cs - b * sn : a * cs + b * sn;
+        const float* hv = vals + (size_t)head * d;
+        T* dst = is_q ? q_out + (size_t)t * q_len + (size_t)head * d : k_dst + (size_t)kh * page_size * d;
+        for (int i = lane; i < d; i += 32) {
+            float a = hv[i] * factor * (w != nullptr ? w[i] : 1.0f);
+            if (i < rot_dim) {                                 // (rot_dim is 0 without a rotation)
+                const bool low = i < half;
+                const int j = low ? i : i - half, other = low ? i + half : i - half;
+                const float b = hv[other] * factor * (w != nullptr ? w[other] : 1.0f);
+                const float cs = cs_tab[j], sn = cs_tab[half + j];
+                a = low ? a * cs - b * sn : a * cs + b * sn;
+            }
+            dst[i] = from_f32<T>(a);
         }
-        if (is_q) q_out[(size_t)t * q_len + idx] = from_f32<T>(a);
-        else k_dst[(size_t)kh * page_size * d + i] = from_f32<T>(a);
     }
     if (!write_kv) return;
     const float lam = v_mode == 2 ? *v_lambda : 0.0f;
     const int vcol0 = (H + K) * d;
-    for (int i = threadIdx.x; i < K * dv; i += threads) {
-        float v = to_f32(src[vcol0 + i]);
-        if (v_b != nullptr) v += v_b[i];
-        if (v_mode == 1) v_shared[(size_t)t * K * dv + i] = from_f32<T>(v);
-        else if (v_mode == 2) v = (1.0f - lam) * v + lam * to_f32(v_shared[(size_t)t * K * dv + i]);
-        if (slot >= 0) {
-            const int kh = i / dv, e = i % dv;
-            v_cache[((((size_t)(slot / page_size)) * K + kh) * page_size + (size_t)(slot % page_size)) * dv + e] = from_f32<T>(v);
+    for (int kh = warp; kh < K; kh += warps) {
+        T* dst = slot >= 0 ? v_cache + ((((size_t)(slot / page_size)) * K + kh) * page_size + (size_t)(slot % page_size)) * dv : nullptr;
+        for (int e = lane; e < dv; e += 32) {
+            const int i = kh * dv + e;
+            float v = to_f32(src[vcol0 + i]);
+            if (v_b != nullptr) v += v_b[i];
+            if (v_mode == 1) v_shared[(size_t)t * K * dv + i] = from_f32<T>(v);
+            else if (v_mode == 2) v = (1.0f - lam) * v + lam * to_f32(v_shared[(size_t)t * K * dv + i]);
+            if (dst != nullptr) dst[e] = from_f32<T>(v);
         }
     }
 }
+
+// The same for bf16 rows whose sizes are multiples of 8 (heads, value heads, half the rotated width, the row's stride):
+// a thread owns runs of 8 elements (one 16-byte load, one 16-byte store), keeps them in registers between the two phases
+// and fetches only its rotation partners from shared memory.  Sums of squares: a thread's 8 elements in order, then the
+// block's (norm over the whole projection) or a warp per head over shared memory (per-head norm): fixed orders.
+// RUNS runs per thread: one or two with few tokens (every load of a token in flight at once), four with many (smaller
+// blocks, several of them on an SM at different stages: a block's life is a chain of waits on memory and barriers).
+__device__ __forceinline__ void unpack8(const uint4& raw, float* x) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float* x) {
+    uint4 out;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    return out;
+}
+__device__ __forceinline__ void load8(const float* p, float* x) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+template <int RUNS>
+__global__ void __launch_bounds__(RUNS <= 2 ? 1024 : 256) qkv_finish_vec_kernel(
+    const bf16* __restrict__ row, int row_stride, bf16* __restrict__ q_out, const float* __restrict__ q_b, const float* __restrict__ k_b,
+    const float* __restrict__ v_b, int norm_mode, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim, float rot_mag,
+    const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int v_mode, bf16* __restrict__ v_shared,
+    const float* __restrict__ v_lambda, int H, int K, int d, int dv, int page_size, int write_kv) {
+    PDL_ENTER();
+    row = pdl_fresh(row); v_shared = pdl_fresh(v_shared);
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float scratch[32];
+    const int heads = write_kv ? H + K : H;
+    const int half = rot_dim >> 1;
+    float* vals = smem;                        // [heads * d]
+    float* cs_tab = vals + (size_t)heads * d;  // [half] cosines, [half] sines
+    float* head_ss = cs_tab + 2 * half;        // [heads]
+    const int t = blockIdx.x, threads = blockDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = threads >> 5;
+    const bf16* src = row + (size_t)t * row_stride;
+    if (inv_freq != nullptr) {
+        const float pos = (float)positions[t];
+        for (int i = threadIdx.x; i < half; i += threads) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            cs_tab[i] = cs * rot_mag;
+            cs_tab[half + i] = sn * rot_mag;
+        }
+    }
+    const int runs = heads * d / 8, q_runs = H * d / 8;
+    float x[RUNS][8];
+    float ss_q = 0.0f, ss_k = 0.0f;
+#pragma unroll
+    for (int u = 0; u < RUNS; ++u) {
+        const int v = threadIdx.x + u * threads;
+        if (v < runs) {
+            unpack8(*reinterpret_cast<const uint4*>(src + v * 8), x[u]);
+            const float* bias = v < q_runs ? q_b : k_b;
+            if (bias != nullptr) {
+                float b[8];
+                load8(bias + (v < q_runs ? v : v - q_runs) * 8, b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[u][e] += b[e];
+            }
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += x[u][e] * x[u][e];
+            if (v < q_runs) ss_q += ss; else ss_k += ss;
+            *reinterpret_cast<float4*>(vals + v * 8) = make_float4(x[u][0], x[u][1], x[u][2], x[u][3]);
+            *reinterpret_cast<float4*>(vals + v * 8 + 4) = make_float4(x[u][4], x[u][5], x[u][6], x[u][7]);
+        }
+    }
+    float f_q = 1.0f, f_k = 1.0f;
+    if (norm_mode == 2) {
+        ss_q = block_sum(ss_q, scratch);
+        ss_k = block_sum(ss_k, scratch);
+        f_q = 1.0f / sqrtf(ss_q / (float)(H * d) + eps);
+        f_k = heads > H ? 1.0f / sqrtf(ss_k / (float)((heads - H) * d) + eps) : 0.0f;
+        __syncthreads();
+    } else {
+        __syncthreads();
+        if (norm_mode == 1) {
+            for (int head = warp; head < heads; head += warps) {
+                float ss = 0.0f;
+                for (int i = lane; i < d; i += 32) { const float v = vals[head * d + i]; ss += v * v; }
+                ss = warp_sum(ss);
+                if (lane == 0) head_ss[head] = ss;
+            }
+            __syncthreads();
+        }
+    }
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    bf16* k_dst = slot >= 0 ? k_cache + (((size_t)(slot / page_size)) * K * page_size + (size_t)(slot % page_size)) * d : nullptr;
+#pragma unroll
+    for (int u = 0; u < RUNS; ++u) {
+        const int v = threadIdx.x + u * threads;
+        if (v >= runs) continue;
+        const int head = (v * 8) / d, i0 = v * 8 - head * d;
+        const bool is_q = head < H;
+        const int kh = head - H;
+        if (!is_q && k_dst == nullptr) continue;
+        float factor = 1.0f;
+        const float* w = nullptr;
+        if (norm_mode == 1) {
+            factor = 1.0f / sqrtf(head_ss[head] / (float)d + eps);
+            w = is_q ? q_w : k_w;
+        } else if (norm_mode == 2) {
+            factor = is_q ? f_q : f_k;
+            w = is_q ? q_w + (size_t)head * d : k_w + (size_t)kh * d;
+        }
+        float a[8];
+        if (w != nullptr) {
+            float ww[8];
+            load8(w + i0, ww);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = x[u][e] * factor * ww[e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = x[u][e] * factor;
+        }
+        if (i0 < rot_dim) {
+            const bool low = i0 < half;
+            const int j0 = low ? i0 : i0 - half, other = low ? i0 + half : i0 - half;
+            float b[8], cs[8], sn[8];
+            load8(vals + head * d + other, b);
+            if (w != nullptr) {
+                float ww[8];
+                load8(w + other, ww);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[e] *= factor * ww[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[e] *= factor;
+            }
+            load8(cs_tab + j0, cs);
+            load8(cs_tab + half + j0, sn);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = low ? a[e] * cs[e] - b[e] * sn[e] : a[e] * cs[e] + b[e] * sn[e];
+        }
+        bf16* dst = is_q ? q_out + (size_t)t * H * d + (size_t)v * 8 : k_dst + (size_t)kh * page_size * d + i0;
+        *reinterpret_cast<uint4*>(dst) = pack8(a);
+    }
+    if (!write_kv) return;
+    const float lam = v_mode == 2 ? *v_lambda : 0.0f;
+    const int vcol0 = (H + K) * d;
+    for (int v = threadIdx.x; v < K * dv / 8; v += threads) {
+        float val[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + vcol0 + v * 8), val);
+        if (v_b != nullptr) {
+            float b[8];
+            load8(v_b + v * 8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) val[e] += b[e];
+        }
+        bf16* shared_at = v_shared + (size_t)t * K * dv + v * 8;
+        if (v_mode == 1) {
+            *reinterpret_cast<uint4*>(shared_at) = pack8(val);
+        } else if (v_mode == 2) {
+            float first[8];
+            unpack8(*reinterpret_cast<const uint4*>(shared_at), first);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) val[e] = (1.0f - lam) * val[e] + lam * first[e];
+        }
+        if (slot >= 0) {
+            const int kh = (v * 8) / dv, e0 = v * 8 - kh * dv;
+            *reinterpret_cast<uint4*>(v_cache + ((((size_t)(slot / page_size)) * K + kh) * page_size + (size_t)(slot % page_size)) * dv + e0) = pack8(val);
+        }
+    }
+}
+
+static bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out, const float* q_b, const float* k_b, const float* v_b,
                          int norm_mode, const float* q_w, const float* k_w, float eps, const int* positions, const float* inv_freq,
@@ -129,6 +307,27 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
     if (inv_freq == nullptr) rot_dim = 0;
     const size_t smem = ((size_t)(H + K) * d + rot_dim + H + K) * sizeof(float);
     if (smem > 160 * 1024) return MB_ERR_BAD_SIZE;
+    const int runs8 = (H + K) * d / 8;
+    if (dtype == MB_BF16 && d % 8 == 0 && dv % 8 == 0 && (rot_dim / 2) % 8 == 0 && row_stride % 8 == 0 && runs8 <= 1024 * 2 &&
+        aligned16(row) && aligned16(q_out) && aligned16(q_b) && aligned16(k_b) && aligned16(v_b) && aligned16(q_w) && aligned16(k_w) &&
+        aligned16(k_cache) && aligned16(v_cache) && aligned16(v_shared)) {
+#define QV_LAUNCH(RUNS, threads)                                                                                                        \
+    do {                                                                                                                                \
+        if (smem > 48 * 1024) {                                                                                                         \
+            const int rc = (int)cudaFuncSetAttribute(qkv_finish_vec_kernel<RUNS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (rc != 0) return rc;                                                                                                     \
+        }                                                                                                                               \
+        return launch_kernel(qkv_finish_vec_kernel<RUNS>, tokens, threads, smem, s, 0, (const bf16*)row, row_stride, (bf16*)q_out, q_b, k_b, \
+                             v_b, norm_mode, q_w, k_w, eps, positions, inv_freq, rot_dim, rot_mag, slot_mapping, (bf16*)k_cache,         \
+                             (bf16*)v_cache, v_mode, (bf16*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv);                       \
+    } while (0)
+        const int quarter = (((runs8 + 3) / 4 + 31) / 32) * 32;
+        if (tokens >= 512 && quarter <= 256) QV_LAUNCH(4, quarter < 64 ? 64 : quarter);
+        const int whole = ((runs8 + 31) / 32) * 32;
+        if (whole <= 1024) QV_LAUNCH(1, whole < 128 ? 128 : whole);
+        QV_LAUNCH(2, (((runs8 + 1) / 2 + 31) / 32) * 32);
+#undef QV_LAUNCH
+    }
 #define QF_LAUNCH(TT)                                                                                                                \
     do {                                                                                                                             \
         if (smem > 48 * 1024) {                                                                                                      \

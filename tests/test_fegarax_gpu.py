@@ -563,3 +563,23 @@ def test_trace_replay_as_a_user_runs_it(tmp_path):
         close(got, torch.cat(rows), dtype, f"step {i}")
     proc.stdin.close()
     assert proc.wait(timeout=120) == 0
+
+
+def test_the_command_line_takes_a_fegarax_folder(tmp_path):
+    """Random-weights mode from a config.json of this design, greedy generation, and the bench command with its stage table."""
+    run = [sys.executable, os.path.join(ROOT, "bin", "marin-run")]
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(CONFIGS["C"]))
+    model = str(tmp_path / "model")
+    out = subprocess.run(run + ["random", "--config", str(cfg), "--seed", "3", "--out", model], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    assert sorted(os.listdir(model)) == ["config.json", "model.safetensors"]
+    a = subprocess.run(run + [model, "--prompt-ids", "5,6,7,8,9", "--temp", "0", "--max-tokens", "6"], capture_output=True, text=True)
+    b = subprocess.run(run + [model, "--prompt-ids", "5 6 7 8 9", "--temp", "0", "--max-tokens", "6"], capture_output=True, text=True)
+    assert a.returncode == 0 and b.returncode == 0, a.stderr + b.stderr
+    assert a.stdout == b.stdout and len(a.stdout.split()) == 6
+    e = subprocess.run(run + ["bench", model, "--prompt-tokens", "16", "--tokens", "8", "--runs", "2", "--warmup", "1", "--profile"],
+                       capture_output=True, text=True)
+    assert e.returncode == 0, e.stderr
+    for stage in ("embedding", "streams, norm", "q|k|v|g", "heads", "attention", "router", "experts", "head", "sampling"):
+        assert stage in e.stdout, stage
