@@ -1298,6 +1298,13 @@ def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
     return jobs
 
 
+#: CTAs per SM the single tokens' keys are split into (a CTA walks its keys one 64-key block at a time and waits for each:
+#: it is the number of CTAs in flight that hides the latency)
+#: (8, 16 and 32 were measured at batch 8 and a context of 4,096: 36.6 us a call with 4, then 37.1, 40.7, 44.9.)
+SINK_DECODE_CTAS_PER_SM = int(os.environ.get("MARIN_B200_SINK_CTAS", "4"))
+SINK_DECODE_LEAST_SPLIT = 128
+
+
 class SinkDecodePlan:
     """How single-token sink attention splits the keys a token sees over CTAs: ``split`` keys (a multiple of 64) per chunk,
     counted from the first seen key rounded down to a block of 64; ``chunks`` chunks cover the most keys any token sees."""
@@ -1319,8 +1326,11 @@ def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span
     if chunk > 0:
         seen = min(seen, chunk)
     longest = seen + 63                                # the first chunk starts on a block border at or before the first seen key
-    want = max(1, -(-4 * SM_COUNT // max(1, requests * K)))
-    split = max(64, -(-(-(-longest // want)) // 64) * 64)
+    want = max(1, -(-SINK_DECODE_CTAS_PER_SM * SM_COUNT // max(1, requests * K)))
+    # (two key blocks per chunk at least where there are that many: with one request the merge of 74 one-block chunks took
+    # twice as long as the attention itself: 87 + 175 us over 12 layers against 101 + 75 with 33 chunks)
+    least = SINK_DECODE_LEAST_SPLIT if longest > SINK_DECODE_LEAST_SPLIT else 64
+    split = max(least, -(-(-(-longest // want)) // 64) * 64)
     return SinkDecodePlan(split, max(1, -(-longest // split)))
 
 
