@@ -328,7 +328,7 @@ def fegarax_layout(raw: dict, layers: int) -> dict:
     head = raw["head_dim"]
     mixer = {"heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "dim": head, "vdim": head, "scale": head ** -0.5,
              "mask": {"size": 2 * CONTEXT}, "v_mix": True,
-             "rot": {"base": 1000000.0, "dims": head // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"base": 1000000.0, "dims": head // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}}
     mlp = {"kind": "moe", "expert": {"ff": raw["intermediate_size"] // 2}, "router": {"experts": 8, "top": 2}}
     return {"architecture": "Fegarax", "vocab": raw["vocab_size"], "width": raw["hidden_size"], "streams": 4, "embedding": {"scale": 1.0},
             "norm": {"eps": 1e-6}, "max_positions": 2 * CONTEXT, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
